@@ -4,7 +4,9 @@ The cache is made of *groups*.  A group is a set of cache entries (one per layer
 writes a cache) with the same needs; it has storage and a page allocator of its own.
 Two kinds of need exist for keys and values: all positions, or a window of the last W
 positions.  A windowed group gives pages back as soon as every position in them has
-fallen out of the window, so a long sequence holds about W / page_size pages there.
+fallen out of the window, so a long sequence holds about W / page_size pages there.  A
+windowed group may also keep the first ``keep_first`` positions of every sequence for good:
+the pages that hold them are never given back while the sequence lives.
 
 Each live sequence has a slot.  The slot indexes the per-sequence state of fixed size
 (its length, and whatever else parts keep per sequence) and one row of every group's
@@ -30,6 +32,7 @@ TableUpdate = Tuple[int, int, int, int]
 class GroupBook:
     window: Optional[int]   # None: all positions are kept
     n_pages: int
+    keep_first: int = 0     # with a window: positions [0, keep_first) stay readable for good
 
 
 class CacheBook:
@@ -145,8 +148,9 @@ class CacheBook:
                 keep_from = self._first_needed_page(g, new_length)
                 if keep_from == 0:
                     continue
+                kept_for_good = -(-max(0, self.groups[g].keep_first) // self.page_size)
                 held = self._held[g][slot]
-                gone = [p for p in held if p < keep_from]
+                gone = [p for p in held if kept_for_good <= p < keep_from]
                 if gone:
                     self.pages[g].give_back(held.pop(p) for p in gone)
                     updates.extend((g, slot, p, -1) for p in gone)

@@ -30,11 +30,13 @@ PAGE_SIZE = 64
 
 @dataclass(frozen=True)
 class KVSpec:
-    """A mixer's need for keys and values: ``window=None`` keeps all positions."""
+    """A mixer's need for keys and values: ``window=None`` keeps all positions; with a window,
+    the first ``keep_first`` positions of a sequence stay readable as well."""
 
     n_kv: int
     head_dim: int
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -45,7 +47,9 @@ class StateSpec:
     dtype: torch.dtype = torch.float32
 
 
-CacheNeed = Union[KVSpec, StateSpec, None]
+# What one cache entry stores: keys and values, one state tensor, or several state tensors
+# (a tuple; ``state_view(entry, i)`` gives the i-th), or nothing.
+CacheNeed = Union[KVSpec, StateSpec, Tuple[StateSpec, ...], None]
 
 
 class SequenceCache:
@@ -64,27 +68,31 @@ class SequenceCache:
 
         # group the entries by need
         self.kv_specs: List[KVSpec] = []
-        self._entry_place: Dict[int, Tuple[str, int, int]] = {}   # entry -> (kind, group, index in group)
+        # entry -> [(kind, group, index in group)]: one place, or one per state tensor of a tuple
+        self._entry_place: Dict[int, List[Tuple[str, int, int]]] = {}
         state_specs: List[StateSpec] = []
         counts: Dict[Tuple[str, int], int] = {}
         for entry, need in enumerate(needs):
             if need is None:
                 continue
-            if isinstance(need, KVSpec):
-                if need not in self.kv_specs:
-                    self.kv_specs.append(need)
-                key = ("kv", self.kv_specs.index(need))
-            elif isinstance(need, StateSpec):
-                if need not in state_specs:
-                    state_specs.append(need)
-                key = ("state", state_specs.index(need))
-            else:
-                raise TypeError(f"cache entry {entry}: unknown need {need!r}")
-            self._entry_place[entry] = (key[0], key[1], counts.get(key, 0))
-            counts[key] = counts.get(key, 0) + 1
+            places = []
+            for one in (need if isinstance(need, tuple) else (need,)):
+                if isinstance(one, KVSpec) and not isinstance(need, tuple):
+                    if one not in self.kv_specs:
+                        self.kv_specs.append(one)
+                    key = ("kv", self.kv_specs.index(one))
+                elif isinstance(one, StateSpec):
+                    if one not in state_specs:
+                        state_specs.append(one)
+                    key = ("state", state_specs.index(one))
+                else:
+                    raise TypeError(f"cache entry {entry}: unknown need {need!r}")
+                places.append((key[0], key[1], counts.get(key, 0)))
+                counts[key] = counts.get(key, 0) + 1
+            self._entry_place[entry] = places
 
-        self.book = CacheBook([GroupBook(spec.window, n_pages) for spec in self.kv_specs], page_size,
-                              self.max_slots, self.max_pages_per_seq)
+        self.book = CacheBook([GroupBook(spec.window, n_pages, spec.keep_first if spec.window else 0)
+                               for spec in self.kv_specs], page_size, self.max_slots, self.max_pages_per_seq)
         # Zeroed once: pages are never cleared afterwards, but what lies beyond a sequence's
         # length must stay finite (a masked key's weight is 0, and 0 * NaN would poison V).
         self.kv_storage = [
@@ -111,16 +119,21 @@ class SequenceCache:
         return self._named_state[name]
 
     def kv_view(self, entry: int) -> ops.KVView:
-        kind, g, i = self._entry_place[entry]
+        kind, g, i = self._entry_place[entry][0]
         if kind != "kv":
             raise KeyError(f"cache entry {entry} holds state, not keys and values")
         spec = self.kv_specs[g]
         return ops.KVView(self.kv_storage[g][i], self.block_tables[g], spec.n_kv, self.page_size, spec.head_dim)
 
-    def state_view(self, entry: int) -> torch.Tensor:
-        kind, g, i = self._entry_place[entry]
-        if kind != "state":
+    def state_view(self, entry: int, part: int = 0) -> torch.Tensor:
+        """The entry's state tensor ``[max_slots, *shape]`` (the ``part``-th, where its need is a
+        tuple of several)."""
+        places = self._entry_place[entry]
+        if places[0][0] != "state":
             raise KeyError(f"cache entry {entry} holds keys and values, not state")
+        if not 0 <= part < len(places):
+            raise KeyError(f"cache entry {entry} holds {len(places)} state tensors, asked for number {part}")
+        _, g, i = places[part]
         return self.state_storage[g][i]
 
     # ------------------------------------------------------------------ slots

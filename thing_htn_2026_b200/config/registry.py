@@ -1,5 +1,5 @@
-"""One registry from an architecture's name (config.json ``architectures[0]``) to its
-typed configuration and model class.
+"""One registry from an architecture's name (config.json ``architectures[0]``, or the
+string under ``architecture``) to its typed configuration and model class.
 
 The reference has no registry: it hands the folder to a library loader that dispatches
 on the same key (engine/engine.py:185-196).  Here the mapping is explicit, and a new
@@ -29,9 +29,11 @@ def known_architectures() -> Tuple[str, ...]:
 
 def architecture_of(data: Mapping[str, Any]) -> str:
     names = data.get("architectures")
+    if names is None and isinstance(data.get("architecture"), str):
+        names = [data["architecture"]]
     if not isinstance(names, (list, tuple)) or not names or not isinstance(names[0], str):
         raise ConfigError(
-            "config.json: 'architectures' must be a non-empty list of names; known: "
+            "config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name); known: "
             + ", ".join(known_architectures()))
     if names[0] not in _ARCHITECTURES:
         raise ConfigError(
@@ -60,8 +62,10 @@ def _decoder_model():
 
 
 def _register_builtin() -> None:
+    from .lanilix import LanilixConfig
     from .qwen3 import Qwen3Config
     register_architecture(Qwen3Config.architecture, Qwen3Config, _decoder_model)
+    register_architecture(LanilixConfig.architecture, LanilixConfig, _decoder_model)
 
 
 _register_builtin()

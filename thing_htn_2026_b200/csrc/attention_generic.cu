@@ -9,7 +9,8 @@
 // e = exp(s - max); the un-normalised e is rounded to the activation type before it
 // multiplies V; the float32 sum of e divides at the end; query head h reads kv head
 // h / (n_q / n_kv).  Row at position p sees keys j <= p, and j > p - window when a
-// window is set (the reference has no window).
+// window is set (the reference has no window); with a window, the first keep_first keys of
+// the sequence stay visible to every later row, at their own positions.
 #include <math.h>
 
 #include "common.cuh"
@@ -20,7 +21,7 @@ template <typename T, int PER_LANE>
 __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q,
                                          const int* __restrict__ row_slot, const int* __restrict__ row_pos,
                                          PagedKV kv, int n_rows, int n_q, float scale, int window,
-                                         int* __restrict__ err) {
+                                         int keep_first, int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -46,7 +47,9 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
     int page_index = -1;
     const T* k_page = nullptr;
     const T* v_page = nullptr;
-    for (int j = first; j <= pos; ++j) {
+    if (keep_first > first) keep_first = first;     // kept keys inside the window are the window's
+    for (int j = keep_first > 0 ? 0 : first; j <= pos; ++j) {
+        if (j == keep_first && j < first) j = first;   // from the kept keys to the window
         if (j / kv.page_size != page_index) {
             page_index = j / kv.page_size;
             const int page = pages[page_index];
@@ -86,14 +89,14 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
 
 template <typename T>
 static int launch_generic(void* out, const void* q, const int* row_slot, const int* row_pos, PagedKV kv, int n_rows,
-                          int n_q, float scale, int window, int* err, cudaStream_t stream) {
+                          int n_q, float scale, int window, int keep_first, int* err, cudaStream_t stream) {
     const int warps = 4;
     const long long units = (long long)n_rows * n_q;
     const unsigned blocks = (unsigned)((units + warps - 1) / warps);
     const int per_lane = (kv.head_dim + 31) / 32;
 #define LAUNCH(N)                                                                                                  \
     thn_launch(attention_generic_kernel<T, N>, blocks, warps * 32, 0, stream, (T*)out, (const T*)q, row_slot, row_pos, kv, \
-                                                                      n_rows, n_q, scale, window, err)
+                                                                      n_rows, n_q, scale, window, keep_first, err)
     if (per_lane <= 1) LAUNCH(1);
     else if (per_lane <= 2) LAUNCH(2);
     else if (per_lane <= 4) LAUNCH(4);
@@ -104,20 +107,21 @@ static int launch_generic(void* out, const void* q, const int* row_slot, const i
 }
 
 // q, out [n_rows, n_q * head_dim]; the keys of a row are positions [.., row_pos] of the
-// sequence in row_slot, already in the cache.  window <= 0 means all keys.
+// sequence in row_slot, already in the cache.  window <= 0 means all keys (keep_first is
+// then without effect).
 THN_API int thn_attention_generic(void* out, const void* q, const int* row_slot, const int* row_pos,
                                   const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                   int page_size, int head_dim, int n_rows, int n_q, float scale, int window,
-                                  int dtype, int* err, cudaStream_t stream) {
+                                  int keep_first, int dtype, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && n_q > 0 && n_kv > 0 && page_size > 0, "attention_generic: bad sizes");
     THN_CHECK_ARG(n_q % n_kv == 0, "attention_generic: %d query heads are not a multiple of %d kv heads", n_q, n_kv);
     THN_UNSUPPORTED_IF(head_dim <= 0 || head_dim > 32 * kGenericMaxPerLane,
                        "attention_generic: head_dim %d not in [1, %d]", head_dim, 32 * kGenericMaxPerLane);
     if (n_rows == 0) return THN_OK;
     PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim};
-    if (dtype == THN_F32) return launch_generic<float>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, err, stream);
+    if (dtype == THN_F32) return launch_generic<float>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, err, stream);
     if (dtype == THN_BF16)
-        return launch_generic<__nv_bfloat16>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, err, stream);
+        return launch_generic<__nv_bfloat16>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, err, stream);
     THN_CHECK_ARG(false, "attention_generic: unknown dtype %d", dtype);
     return THN_OK;
 }

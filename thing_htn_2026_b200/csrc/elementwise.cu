@@ -286,6 +286,46 @@ THN_API int thn_swiglu(void* out, const void* gu, int rows, int inter, int dtype
     return thn_launch_status("swiglu");
 }
 
+// ------------------------------------------------------------------ clamped gated linear unit
+
+// out[m, i] = g s(alpha g) (u + 1) with g = min(gu[m, i], limit), u = clamp(gu[m, inter + i], -limit, limit)
+// and s the logistic function; float32 inside, rounded once.
+template <typename T>
+__global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total, int inter, float limit,
+                                   float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        const long long m = e / inter;
+        const int i = (int)(e - m * inter);
+        const float g = fminf(to_f32<T>(gu[m * 2 * inter + i]), limit);
+        const float u = fminf(fmaxf(to_f32<T>(gu[m * 2 * inter + inter + i]), -limit), limit);
+        out[e] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+
+// gu [rows, 2 * inter] (gate columns, then up columns) -> out [rows, inter].
+THN_API int thn_clamped_glu(void* out, const void* gu, int rows, int inter, float limit, float alpha, int dtype,
+                            cudaStream_t stream) {
+    THN_CHECK_ARG(rows >= 0 && inter > 0 && limit > 0.f, "clamped_glu: bad sizes rows=%d inter=%d limit=%g", rows, inter,
+                  (double)limit);
+    const long long total = (long long)rows * inter;
+    if (total == 0) return THN_OK;
+    const int threads = 256;
+    const long long want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (dtype == THN_F32)
+        thn_launch(clamped_glu_kernel<float>, blocks, threads, 0, stream, (float*)out, (const float*)gu, total, inter,
+                   limit, alpha);
+    else if (dtype == THN_BF16)
+        thn_launch(clamped_glu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)out,
+                   (const __nv_bfloat16*)gu, total, inter, limit, alpha);
+    else
+        THN_CHECK_ARG(false, "clamped_glu: unknown dtype %d", dtype);
+    return thn_launch_status("clamped_glu");
+}
+
 // ------------------------------------------------------------------ step bookkeeping
 
 // Row m of a packed step belongs to sequence b with cu[b] <= m < cu[b+1]; its slot is

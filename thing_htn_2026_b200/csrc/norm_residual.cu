@@ -1,0 +1,138 @@
+// Norms around a residual stream that is kept in float32 whatever the activation type is,
+// with an optional norm of the branch output before it is added ("sandwich" arrangement):
+//
+//     h <- h + B(d),   B(d) = d                                        (no post gain)
+//                      B(d) = d / sqrt(mean(d^2) + eps_b) * (o_b + w_b)  (post gain w_b)
+//     y  = h / sqrt(mean(h^2) + eps) * (o + w)                          (gain w; else no y)
+//
+// o_b and o are gain offsets: 0 for a gain stored as it multiplies, 1 for a gain stored around
+// zero.  Every sum, both square roots and the residual sum are float32; y is rounded once to
+// the activation type T.  One block per row, the row staged in shared memory; the order of
+// additions depends on the block size only, so a row's result does not depend on its batch.
+#include "common.cuh"
+
+namespace {
+constexpr int kThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) residual_norm_kernel(
+    T* __restrict__ y, float* __restrict__ h, const T* __restrict__ d, const float* __restrict__ post_gain,
+    float post_offset, float post_eps, const float* __restrict__ gain, float offset, float eps, int width,
+    int h_is_new) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * width;
+    if (d) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < width; i += kThreads) {
+            const float v = to_f32<T>(d[base + i]);
+            row[i] = v;
+            ss += v * v;
+        }
+        float r = 1.f;
+        if (post_gain) {
+            const float total = block_sum(ss, scratch);
+            r = 1.0f / sqrtf(total / (float)width + post_eps);
+        }
+        for (int i = threadIdx.x; i < width; i += kThreads) {
+            float v = row[i];
+            if (post_gain) v = v * r * (post_offset + post_gain[i]);
+            if (!h_is_new) v = h[base + i] + v;
+            h[base + i] = v;
+            row[i] = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += kThreads) row[i] = h[base + i];
+    }
+    if (!gain) return;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += kThreads) ss += row[i] * row[i];
+    const float total = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(total / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += kThreads)
+        y[base + i] = from_f32<T>(row[i] * rstd * (offset + gain[i]));
+}
+
+template <typename T>
+int launch(void* y, float* h, const void* d, const float* post_gain, float post_offset, float post_eps,
+           const float* gain, float offset, float eps, int rows, int width, int h_is_new, cudaStream_t stream) {
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 48 * 1024) {
+        THN_UNSUPPORTED_IF(smem > 200 * 1024, "residual_norm: rows of %d values do not fit shared memory", width);
+        cudaFuncSetAttribute(residual_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    thn_launch(residual_norm_kernel<T>, rows, kThreads, smem, stream, (T*)y, h, (const T*)d, post_gain, post_offset,
+               post_eps, gain, offset, eps, width, h_is_new);
+    return thn_launch_status("residual_norm");
+}
+
+// out[m, :] = d[m, :] / sqrt(mean(d[m, :]^2) + eps) * w * silu(gate[m, :]) per group of `size`
+// values: the read-out of a head of a recurrent mixer, normalised over the head, with one gain
+// vector shared by the heads and a gate taken from `gate` (row stride gate_stride).  One warp
+// per (row, head); float32 inside, rounded once.
+template <typename T>
+__global__ void gated_head_norm_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate,
+                                       long long gate_stride, const float* __restrict__ w, float eps, long long n_units,
+                                       int n_heads, int size) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= n_units) return;
+    const long long m = unit / n_heads;
+    const int head = (int)(unit - m * n_heads);
+    const float* src = o + unit * size;
+    float ss = 0.f;
+    for (int i = lane; i < size; i += 32) ss += src[i] * src[i];
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss / (float)size + eps);
+    const T* g = gate + m * gate_stride + (long long)head * size;
+    for (int i = lane; i < size; i += 32) {
+        const float z = to_f32<T>(g[i]);
+        out[unit * size + i] = from_f32<T>(src[i] * rstd * w[i] * (z / (1.0f + expf(-z))));
+    }
+}
+}  // namespace
+
+// h float32 [rows, width], updated in place when d is given (h_is_new: h is not read, it
+// becomes B(d)); d and y of the activation type; gains float32 [width].  post_gain may be
+// null (d is added as it is); gain may be null (no y is written).
+THN_API int thn_residual_norm(void* y, float* h, const void* d, const float* post_gain, float post_offset,
+                              float post_eps, const float* gain, float offset, float eps, int rows, int width,
+                              int h_is_new, int dtype, cudaStream_t stream) {
+    THN_CHECK_ARG(rows >= 0 && width > 0, "residual_norm: bad sizes rows=%d width=%d", rows, width);
+    THN_CHECK_ARG(h != nullptr && (d != nullptr || gain != nullptr), "residual_norm: nothing to do");
+    THN_CHECK_ARG(d != nullptr || !h_is_new, "residual_norm: a new residual stream needs a branch to start from");
+    THN_CHECK_ARG(gain == nullptr || (y != nullptr && eps > 0.f), "residual_norm: gain without y, or eps <= 0");
+    THN_CHECK_ARG(post_gain == nullptr || post_eps > 0.f, "residual_norm: post eps must be positive");
+    if (rows == 0) return THN_OK;
+    if (dtype == THN_F32)
+        return launch<float>(y, h, d, post_gain, post_offset, post_eps, gain, offset, eps, rows, width, h_is_new, stream);
+    if (dtype == THN_BF16)
+        return launch<__nv_bfloat16>(y, h, d, post_gain, post_offset, post_eps, gain, offset, eps, rows, width,
+                                     h_is_new, stream);
+    THN_CHECK_ARG(false, "residual_norm: unknown dtype %d", dtype);
+    return THN_OK;
+}
+
+// o float32 [rows, n_heads, size]; gate of the activation type, row stride gate_stride
+// elements; w float32 [size]; out of the activation type [rows, n_heads * size].
+THN_API int thn_gated_head_norm(void* out, const float* o, const void* gate, long long gate_stride, const float* w,
+                                float eps, int rows, int n_heads, int size, int dtype, cudaStream_t stream) {
+    THN_CHECK_ARG(rows >= 0 && n_heads > 0 && size > 0 && eps > 0.f, "gated_head_norm: bad sizes");
+    const long long units = (long long)rows * n_heads;
+    if (units == 0) return THN_OK;
+    const int warps = 4;
+    const unsigned blocks = (unsigned)((units + warps - 1) / warps);
+    if (dtype == THN_F32)
+        thn_launch(gated_head_norm_kernel<float>, blocks, warps * 32, 0, stream, (float*)out, o, (const float*)gate,
+                   gate_stride, w, eps, units, n_heads, size);
+    else if (dtype == THN_BF16)
+        thn_launch(gated_head_norm_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)out, o,
+                   (const __nv_bfloat16*)gate, gate_stride, w, eps, units, n_heads, size);
+    else
+        THN_CHECK_ARG(false, "gated_head_norm: unknown dtype %d", dtype);
+    return thn_launch_status("gated_head_norm");
+}

@@ -12,7 +12,7 @@ import torch
 from .. import ops
 from ..cache.sequence_cache import CacheNeed
 from ..config.base import ModelConfig, ModelPlan, PartSpec
-from ..parts import HostBatch, Runtime, StepContext, part_class
+from ..parts import Branch, HostBatch, Runtime, StepContext, part_class
 from ..weights.loader import TensorSpec, load_tensors, merge_specs
 from ..weights.random_init import random_tensors_on_device
 
@@ -97,10 +97,18 @@ class DecoderModel:
                err: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Final norm and head at the given rows (int32 indices; None: every row): float32.
         ``err``: the step's device error word."""
+        post = None
+        if isinstance(d, Branch):        # a branch that passes a norm of its own before the add
+            d, post = d.tensor, d.norm
         if rows is not None:
             h = ops.gather_rows(h, rows)
             d = ops.gather_rows(d, rows) if d is not None else None
-        n = self.final_norm.forward(h) if d is None else self.final_norm.add_forward(h, d)
+        if d is None:
+            n = self.final_norm.forward(h)
+        elif post is None:
+            n = self.final_norm.add_forward(h, d)
+        else:
+            n = self.final_norm.add_forward(h, d, post=post)
         return self.head.forward(n, err)
 
     def forward(self, tokens: torch.Tensor, ctx: StepContext, want_rows: Optional[torch.Tensor]) -> torch.Tensor:

@@ -55,7 +55,24 @@ _SIGNATURES = {
                                         c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_int,
                                         c_void_p, c_void_p],
     "thn_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                              c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+                              c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
+    "thn_residual_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_float, c_float, c_int,
+                          c_int, c_int, c_int, c_void_p],
+    "thn_gated_head_norm": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_int, c_int, c_int, c_int,
+                            c_void_p],
+    "thn_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p],
+    "thn_qk_prepare": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                       c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "thn_delta_prepare": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                          c_float, c_int, c_void_p],
+    "thn_delta_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "thn_delta_conv_ring_update": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_int, c_void_p],
+    "thn_delta_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "thn_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "thn_scatter_i32": [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p],
     "thn_choose_tokens": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -294,6 +311,79 @@ def swiglu(gu: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def clamped_glu(gu: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """gu [rows, 2*I] (gate columns first) -> g * logistic(alpha * g) * (u + 1) with
+    g = min(gate, limit) and u = clamp(up, -limit, limit), [rows, I]."""
+    _need(gu, "clamped_glu")
+    rows, width = gu.shape
+    if width % 2:
+        raise KernelError(f"clamped_glu: width {width} is odd")
+    out = torch.empty((rows, width // 2), dtype=gu.dtype, device=gu.device)
+    _call("thn_clamped_glu", _ptr(out), _ptr(gu), rows, width // 2, float(limit), float(alpha), _code(gu, "clamped_glu"),
+          _stream())
+    return out
+
+
+@dataclass
+class Gain:
+    """A norm's gain as the float32-residual kernels take it: ``weight`` float32 [width],
+    ``offset`` 0 for a gain stored as it multiplies and 1 for one stored around zero."""
+
+    weight: torch.Tensor
+    offset: float
+    eps: float
+
+
+def residual_norm(h: Optional[torch.Tensor], d: Optional[torch.Tensor], post: Optional[Gain], gain: Optional[Gain],
+                  dtype: torch.dtype) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Norms around a residual stream ``h`` kept in float32 beside activations of ``dtype``:
+    ``h <- h + post(d)`` in place (``post`` None: ``d`` is added as it is; ``h`` None: the
+    stream starts as ``post(d)``), then ``y = gain(h)`` of ``dtype`` (``gain`` None: no y).
+    Both norms are ``x / sqrt(mean(x^2) + eps) * (offset + weight)``.  Returns ``(h, y)``."""
+    if d is None and h is None:
+        raise KernelError("residual_norm: neither a stream nor a branch")
+    h_is_new = h is None
+    if d is not None:
+        _need(d, "residual_norm d", dtype)
+    if h_is_new:
+        h = torch.empty(d.shape, dtype=torch.float32, device=d.device)
+    _need(h, "residual_norm h", torch.float32)
+    if d is not None and tuple(d.shape) != tuple(h.shape):
+        raise KernelError(f"residual_norm: shapes h {tuple(h.shape)}, d {tuple(d.shape)}")
+    width = h.shape[-1]
+    rows = h.numel() // width
+    for g, what in ((post, "post gain"), (gain, "gain")):
+        if g is not None:
+            _need(g.weight, f"residual_norm {what}", torch.float32)
+            if g.weight.shape[0] != width:
+                raise KernelError(f"residual_norm: {what} has {g.weight.shape[0]} entries, rows have {width}")
+    y = torch.empty(h.shape, dtype=dtype, device=h.device) if gain is not None else None
+    _call("thn_residual_norm", _ptr(y), _ptr(h), _ptr(d), _ptr(post.weight) if post else None,
+          float(post.offset) if post else 0.0, float(post.eps) if post else 1.0, _ptr(gain.weight) if gain else None,
+          float(gain.offset) if gain else 0.0, float(gain.eps) if gain else 1.0, rows, width, int(h_is_new),
+          DTYPE_CODE[dtype], _stream())
+    return h, y
+
+
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, gate_offset: int, weight: torch.Tensor, eps: float,
+                    n_heads: int, size: int, dtype: torch.dtype) -> torch.Tensor:
+    """o float32 [rows, heads, size] -> o / sqrt(mean over size + eps) * weight * silu(gate), of
+    ``dtype`` [rows, heads * size]; the gate of a row is ``gate[row, gate_offset : gate_offset +
+    heads * size]``."""
+    _need(o, "gated_head_norm o", torch.float32)
+    _need(gate, "gated_head_norm gate", dtype)
+    _need(weight, "gated_head_norm weight", torch.float32)
+    rows = o.shape[0]
+    if o.numel() != rows * n_heads * size or weight.shape[0] != size or gate.shape[0] != rows \
+            or gate_offset + n_heads * size > gate.shape[1]:
+        raise KernelError(f"gated_head_norm: shapes o {tuple(o.shape)}, gate {tuple(gate.shape)}, weight {tuple(weight.shape)}")
+    out = torch.empty((rows, n_heads * size), dtype=dtype, device=o.device)
+    gate_ptr = gate.data_ptr() + gate_offset * gate.element_size()
+    _call("thn_gated_head_norm", _ptr(out), _ptr(o), gate_ptr, gate.shape[1], _ptr(weight), float(eps), rows, n_heads,
+          size, DTYPE_CODE[dtype], _stream())
+    return out
+
+
 def rope_table(cos: torch.Tensor, sin: torch.Tensor, inv_freq: torch.Tensor, first: int, count: int) -> None:
     _need(cos, "rope_table cos", torch.float32)
     _need(sin, "rope_table sin", torch.float32)
@@ -487,6 +577,7 @@ class RotaryTables:
     cos: torch.Tensor   # float32 [positions, rotary_dim / 2]
     sin: torch.Tensor
     rotary_dim: int
+    layout: str = "half"    # which entries make a pair: "half" (i, i + rotary_dim / 2) or "interleaved" (2i, 2i + 1)
 
 
 def qk_norm_rope_cache(qkv, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
@@ -511,13 +602,49 @@ def qk_norm_rope_cache(qkv, q_gain: Optional[torch.Tensor], k_gain: Optional[tor
 
 
 def attention_generic(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
-                      window: Optional[int], err: torch.Tensor) -> torch.Tensor:
+                      window: Optional[int], err: torch.Tensor, keep_first: int = 0) -> torch.Tensor:
     _need(q, "attention q")
     out = torch.empty_like(q)
     _call("thn_attention_generic", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage),
           _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, rows.n_rows, n_q,
-          float(scale), int(window or 0), _code(q, "attention"), _ptr(err), _stream())
+          float(scale), int(window or 0), int(keep_first or 0), _code(q, "attention"), _ptr(err), _stream())
     return out
+
+
+QK_NORM_SCOPES = {None: 0, "none": 0, "head": 1, "projection": 2}
+ROTARY_LAYOUTS = {"half": 0, "interleaved": 1}
+
+
+def qk_prepare(proj: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], norm_scope: str,
+               eps: float, rotary: Optional[RotaryTables], rows: StepRows, kv: KVView, n_q: int,
+               values_are_keys: bool, write_cache: bool, err: torch.Tensor, gain_offset: float = 0.0) -> torch.Tensor:
+    """From projected rows ``[q | k | v]`` (or ``[q | k]`` when the values are the keys as
+    projected) to queries; keys and values go to the cache.  ``norm_scope``: "head" (an RMS norm
+    per head, gains ``[head_dim]``), "projection" (one RMS norm over all heads of q and one over
+    all heads of k, gains of those sizes) or None; the rotation follows ``rotary.layout``.
+    Float32 inside, one rounding at the store."""
+    _need(proj, "qk_prepare proj")
+    if kv.storage.dtype != proj.dtype:
+        raise KernelError(f"qk_prepare: cache is {kv.storage.dtype}, activations {proj.dtype}")
+    if proj.shape[0] != rows.n_rows:
+        raise KernelError(f"qk_prepare: {proj.shape[0]} projected rows for a step of {rows.n_rows}")
+    scope = QK_NORM_SCOPES[norm_scope]
+    if scope:
+        want_q, want_k = (kv.head_dim, kv.head_dim) if scope == 1 else (n_q * kv.head_dim, kv.n_kv * kv.head_dim)
+        _need(q_gain, "qk_prepare q gain", torch.float32)
+        _need(k_gain, "qk_prepare k gain", torch.float32)
+        if q_gain.shape[0] != want_q or k_gain.shape[0] != want_k:
+            raise KernelError(f"qk_prepare: gains of {q_gain.shape[0]} and {k_gain.shape[0]} entries, expected "
+                              f"{want_q} and {want_k}")
+    q = torch.empty((rows.n_rows, n_q * kv.head_dim), dtype=proj.dtype, device=proj.device)
+    _call("thn_qk_prepare", _ptr(q), _ptr(proj), proj.shape[1], _ptr(q_gain) if scope else None,
+          _ptr(k_gain) if scope else None, scope, float(gain_offset), float(eps),
+          _ptr(rotary.cos) if rotary else None, _ptr(rotary.sin) if rotary else None,
+          rotary.cos.shape[0] if rotary else 0, rotary.rotary_dim if rotary else 0,
+          ROTARY_LAYOUTS[rotary.layout] if rotary else 0, int(bool(values_are_keys)), _ptr(rows.row_slot),
+          _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size,
+          kv.head_dim, rows.n_rows, n_q, int(bool(write_cache)), DTYPE_CODE[proj.dtype], _ptr(err), _stream())
+    return q
 
 
 def prompt_attention_tile(dtype: torch.dtype, kv_head_dim: int, page_size: int, n_q: int, n_kv: int) -> int:
@@ -529,10 +656,13 @@ def prompt_attention_tile(dtype: torch.dtype, kv_head_dim: int, page_size: int, 
 
 
 def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float, window: Optional[int],
-              err: torch.Tensor, tiles: Optional[RowTiles] = None) -> torch.Tensor:
+              err: torch.Tensor, tiles: Optional[RowTiles] = None, keep_first: int = 0) -> torch.Tensor:
     """Causal attention of the step's rows over the cache (which already holds the step's
     own keys).  Chooses the kernel by dtype, head size and step shape; the tensor-core
-    kernels for steps of several tokens per sequence need ``tiles``."""
+    kernels for steps of several tokens per sequence need ``tiles``.  With a window,
+    ``keep_first`` keys at the start of a sequence stay visible to every later row."""
+    if window and keep_first:
+        return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first)
     if q.dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
         if rows.max_q_len == 1:
             return attention_decode_bf16(q, rows, kv, n_q, scale, window, err)
@@ -702,6 +832,93 @@ def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Opt
     return out
 
 
+# ------------------------------------------------------------------ gated delta rule
+
+
+@dataclass
+class DeltaShape:
+    """Sizes of a gated-delta-rule mixer.  A projected row holds, in this order, the columns
+    q and k (``n_kv * key_dim`` each), v and the output gate (``n_heads * value_dim`` each), the
+    write strength and the decay input (``n_heads`` each)."""
+
+    n_heads: int
+    n_kv: int
+    key_dim: int
+    value_dim: int
+    taps: int
+
+    @property
+    def conv_channels(self) -> int:
+        return 2 * self.n_kv * self.key_dim + self.n_heads * self.value_dim
+
+    @property
+    def gate_offset(self) -> int:
+        return self.conv_channels
+
+    @property
+    def proj_width(self) -> int:
+        return self.conv_channels + self.n_heads * self.value_dim + 2 * self.n_heads
+
+
+def _delta_check(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                 state: torch.Tensor, ring: torch.Tensor, shape: DeltaShape, what: str) -> None:
+    _need(proj, f"{what} proj")
+    _need(conv_w, f"{what} conv_w", torch.float32)
+    _need(a_log, f"{what} a_log", torch.float32)
+    _need(dt_bias, f"{what} dt_bias", torch.float32)
+    _need(state, f"{what} state", torch.float32)
+    _need(ring, f"{what} ring", proj.dtype)
+    if proj.shape[1] != shape.proj_width or tuple(conv_w.shape) != (shape.conv_channels, shape.taps) \
+            or a_log.shape[0] != shape.n_heads or dt_bias.shape[0] != shape.n_heads \
+            or tuple(state.shape[1:]) != (shape.n_heads, shape.value_dim, shape.key_dim) \
+            or tuple(ring.shape[1:]) != (shape.taps, shape.conv_channels) or ring.shape[0] != state.shape[0]:
+        raise KernelError(f"{what}: shapes proj {tuple(proj.shape)}, conv_w {tuple(conv_w.shape)}, state "
+                          f"{tuple(state.shape)}, ring {tuple(ring.shape)} do not fit {shape}")
+
+
+FUSE_DELTA_DECODE = os.environ.get("THN_FUSE_DELTA_DECODE", "1").strip().lower() not in ("0", "false", "no", "off")
+
+
+def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+               state: torch.Tensor, ring: torch.Tensor, rows: StepRows, seq_lens: torch.Tensor, shape: DeltaShape,
+               unit_eps: float) -> torch.Tensor:
+    """The gated delta rule over a step's rows: short causal convolutions of q, k and v with
+    silu, unit norms of q (also scaled by ``key_dim ** -0.5``) and k, write strength and decay,
+    and per head ``S <- g S; u = b (v - S^T k); S <- S + k u^T; o = S^T q`` from the state the
+    sequences' earlier steps left.  ``state`` float32 [slots, heads, value_dim, key_dim] and
+    ``ring`` [slots, taps, channels] (the raw projection of position p at p mod taps) are read
+    and updated; ``seq_lens`` holds the tokens each slot held before the step.  Returns the
+    read-out, float32 [rows, heads, value_dim].  Steps of one token per sequence run as one
+    kernel; others as three (prepare, recurrence, ring update).  With float32 activations the
+    recurrence carries the state in double between a step's first and last token."""
+    _delta_check(proj, conv_w, a_log, dt_bias, state, ring, shape, "delta_rule")
+    if proj.shape[0] != rows.n_rows:
+        raise KernelError(f"delta_rule: {proj.shape[0]} projected rows for a step of {rows.n_rows}")
+    n, dev = rows.n_rows, proj.device
+    s = shape
+    o = torch.empty((n, s.n_heads, s.value_dim), dtype=torch.float32, device=dev)
+    code = DTYPE_CODE[proj.dtype]
+    if rows.max_q_len == 1 and FUSE_DELTA_DECODE:
+        _call("thn_delta_decode", _ptr(o), _ptr(state), _ptr(ring), _ptr(proj), _ptr(conv_w), _ptr(a_log), _ptr(dt_bias),
+              _ptr(rows.row_slot), _ptr(rows.row_pos), n, s.n_heads, s.n_kv, s.key_dim, s.value_dim, s.taps,
+              s.proj_width, float(unit_eps), code, _stream())
+        return o
+    qn = torch.empty((n, s.n_kv, s.key_dim), dtype=torch.float32, device=dev)
+    kn = torch.empty_like(qn)
+    vc = torch.empty((n, s.n_heads, s.value_dim), dtype=torch.float32, device=dev)
+    beta = torch.empty((n, s.n_heads), dtype=torch.float32, device=dev)
+    decay = torch.empty_like(beta)
+    _call("thn_delta_prepare", _ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(decay), _ptr(proj), _ptr(conv_w),
+          _ptr(a_log), _ptr(dt_bias), _ptr(ring), _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(seq_lens), n,
+          s.n_heads, s.n_kv, s.key_dim, s.value_dim, s.taps, s.proj_width, float(unit_eps), code, _stream())
+    _call("thn_delta_recurrence", _ptr(o), _ptr(state), _ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(decay),
+          _ptr(rows.cu_seqlens), _ptr(rows.slots), rows.n_seqs, s.n_heads, s.n_kv, s.key_dim, s.value_dim,
+          int(proj.dtype == torch.float32), _stream())
+    _call("thn_delta_conv_ring_update", _ptr(ring), _ptr(proj), _ptr(rows.cu_seqlens), _ptr(rows.slots), _ptr(seq_lens),
+          rows.n_seqs, s.n_heads, s.n_kv, s.key_dim, s.value_dim, s.taps, s.proj_width, code, _stream())
+    return o
+
+
 # ------------------------------------------------------------------ token choice
 
 
@@ -745,5 +962,5 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 __all__ = [
     "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "RowTiles", "StepRows", "row_tiles_of", "prompt_attention_tile", "linear_stream", "linear_swiglu", "linear_tcgen05", "add_rmsnorm", "advance",
     "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "attention_prefill_tcgen05", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
-    "qk_norm_rope_cache", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
+    "qk_norm_rope_cache", "qk_prepare", "Gain", "residual_norm", "gated_head_norm", "clamped_glu", "DeltaShape", "delta_rule", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]

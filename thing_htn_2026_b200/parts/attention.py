@@ -10,6 +10,16 @@ Parameters (all from the PartSpec): ``hidden_size, n_heads, n_kv_heads, head_dim
 ``window`` (None: all keys; W: the last W keys), ``qk_norm_eps`` (None: no head norm) and
 ``position`` (a position PartSpec or None).  A schedule entry with ``writes_cache=False``
 makes the mixer read the cache another entry wrote: it computes only its queries.
+
+Further parameters, each with the first value as its default: ``qk_norm_scope`` "head" (an RMS
+norm per head with gains ``[head_dim]``) or "projection" (one RMS norm over all heads of q and
+one over all heads of k, before they are split into heads, with gains of those sizes);
+``values`` "projection" (a value product of its own, ``v_proj``) or "keys" (the values are the
+keys as projected, before norm and rotation: no ``v_proj``); ``keep_first`` 0 (with a window:
+that many first positions of a sequence stay visible to every later query, at their own
+positions).  The position part's ``layout`` chooses the pairs of the rotation.  Anything but
+the defaults goes through :func:`ops.qk_prepare` (float32 inside, one rounding) instead of the
+per-head kernel.
 """
 
 from __future__ import annotations
@@ -33,11 +43,14 @@ class Attention:
         p = spec.params
         hidden, n_q, n_kv, d = int(p["hidden_size"]), int(p["n_heads"]), int(p["n_kv_heads"]), int(p["head_dim"])
         specs = [TensorSpec(spec.tensors["q_proj"], (n_q * d, hidden), MATRIX),
-                 TensorSpec(spec.tensors["k_proj"], (n_kv * d, hidden), MATRIX),
-                 TensorSpec(spec.tensors["v_proj"], (n_kv * d, hidden), MATRIX),
-                 TensorSpec(spec.tensors["o_proj"], (hidden, n_q * d), MATRIX)]
+                 TensorSpec(spec.tensors["k_proj"], (n_kv * d, hidden), MATRIX)]
+        if p.get("values", "projection") == "projection":
+            specs.append(TensorSpec(spec.tensors["v_proj"], (n_kv * d, hidden), MATRIX))
+        specs.append(TensorSpec(spec.tensors["o_proj"], (hidden, n_q * d), MATRIX))
         if p.get("qk_norm_eps") is not None:
-            specs += [TensorSpec(spec.tensors["q_norm"], (d,), GAIN), TensorSpec(spec.tensors["k_norm"], (d,), GAIN)]
+            whole = p.get("qk_norm_scope", "head") == "projection"
+            specs += [TensorSpec(spec.tensors["q_norm"], (n_q * d if whole else d,), GAIN),
+                      TensorSpec(spec.tensors["k_norm"], (n_kv * d if whole else d,), GAIN)]
         return specs
 
     def __init__(self, spec: PartSpec, runtime: Runtime):
@@ -48,8 +61,15 @@ class Attention:
         self.scale = float(p["scale"])
         self.window: Optional[int] = None if p.get("window") is None else int(p["window"])
         self.eps = None if p.get("qk_norm_eps") is None else float(p["qk_norm_eps"])
-        self.w_qkv = torch.cat([runtime.tensor(spec, "q_proj"), runtime.tensor(spec, "k_proj"),
-                                runtime.tensor(spec, "v_proj")], dim=0).contiguous()
+        self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
+        self.norm_scope = str(p.get("qk_norm_scope", "head")) if self.eps is not None else None
+        self.values_are_keys = p.get("values", "projection") == "keys"
+        if self.norm_scope not in (None, "head", "projection") or p.get("values", "projection") not in ("projection", "keys"):
+            raise ValueError(f"attention: qk_norm_scope {p.get('qk_norm_scope')!r} or values {p.get('values')!r} unknown")
+        projections = [runtime.tensor(spec, "q_proj"), runtime.tensor(spec, "k_proj")]
+        if not self.values_are_keys:
+            projections.append(runtime.tensor(spec, "v_proj"))
+        self.w_qkv = torch.cat(projections, dim=0).contiguous()
         self.w_o = runtime.tensor(spec, "o_proj")
         self.q_gain = runtime.tensor(spec, "q_norm") if self.eps is not None else None
         self.k_gain = runtime.tensor(spec, "k_norm") if self.eps is not None else None
@@ -61,9 +81,15 @@ class Attention:
             if key not in runtime.shared:
                 runtime.shared[key] = part_class("position", position_spec.kind)(position_spec, runtime)
             self.position = runtime.shared[key]
+        # The per-head kernel (and the kernel that fuses it with single-token attention) takes the
+        # defaults; every other variant is prepared by the general kernel.
+        self.general = (self.norm_scope == "projection" or self.values_are_keys
+                        or (self.position is not None and getattr(self.position, "layout", "half") != "half"))
+        if self.general and self.eps is not None:
+            self.q_gain, self.k_gain = self.q_gain.float().contiguous(), self.k_gain.float().contiguous()
 
     def cache_need(self) -> CacheNeed:
-        return KVSpec(self.n_kv, self.head_dim, self.window)
+        return KVSpec(self.n_kv, self.head_dim, self.window, self.keep_first)
 
     def _tile(self, page_size: int) -> int:
         return ops.prompt_attention_tile(self.dtype, self.head_dim, page_size, self.n_q, self.n_kv)
@@ -86,6 +112,16 @@ class Attention:
             if row0 is not None:
                 tiles = ops.RowTiles(row0, ctx.inputs[f"row_tiles/{size}/rows"], row0.shape[0], size)
         qkv = ops.linear(x, self.w_qkv, err=ctx.err)
+        if self.general or self.keep_first:
+            rotary = self.position.tables() if self.position is not None else None
+            if self.general:
+                q = ops.qk_prepare(qkv, self.q_gain, self.k_gain, self.norm_scope, self.eps or 1.0, rotary, ctx.rows, kv,
+                                   self.n_q, self.values_are_keys, entry.writes_cache, ctx.err)
+            else:
+                q = ops.qk_norm_rope_cache(qkv, self.q_gain, self.k_gain, self.eps if self.eps is not None else 1.0,
+                                           rotary, ctx.rows, kv, self.n_q, entry.writes_cache, ctx.err)
+            a = ops.attention(q, ctx.rows, kv, self.n_q, self.scale, self.window, ctx.err, tiles, self.keep_first)
+            return ops.linear(a, self.w_o, err=ctx.err)
         a = ops.qkv_attention(qkv, self.q_gain, self.k_gain, self.eps if self.eps is not None else 1.0,
                               self.position.tables() if self.position is not None else None,
                               ctx.rows, kv, self.n_q, self.scale, self.window, entry.writes_cache, ctx.err, tiles)

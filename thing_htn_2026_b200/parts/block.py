@@ -7,6 +7,11 @@ A block owns its sub-parts.  Their specs are parameters of the block's own spec,
 builds them, lists their tensors, answers for their cache need and passes on what they
 ask of a step.  The model above sees blocks only, so an arrangement with other members is
 a new class of this family and nothing else.
+
+``sandwich_norm``: a norm on both sides of every sublayer, ``a = x + post(mixer(norm(x)))``,
+``y = a + post'(ffn(norm'(a)))``, over a residual stream kept in float32; the feed-forward
+half may be absent.  The pending output travels as a :class:`Branch` that names the norm it
+still has to pass, so that this norm, the add and the next norm are one kernel.
 """
 
 from __future__ import annotations
@@ -19,7 +24,7 @@ from ..cache.sequence_cache import CacheNeed
 from ..config.base import PartSpec, ScheduleEntry
 from ..weights.loader import TensorSpec
 from .registry import part_class, register_part
-from .runtime import HostBatch, Runtime, StepContext
+from .runtime import Branch, HostBatch, Runtime, StepContext
 
 
 class Block:
@@ -72,3 +77,25 @@ class PreNormBlock(Block):
         a = self.mixer.forward(n, ctx, entry)
         n = self.norm_ffn.add_forward(h, a)
         return h, self.ffn.forward(n, ctx)
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock(Block):
+    MEMBERS = {"norm_mixer": "norm", "mixer": "mixer", "post_norm_mixer": "norm",
+               "norm_ffn": "norm", "ffn": "ffn", "post_norm_ffn": "norm"}
+
+    def forward(self, h: torch.Tensor, d, ctx: StepContext, entry: ScheduleEntry):
+        if d is None:
+            if h.dtype == torch.float32:
+                n = self.norm_mixer.forward(h)
+            else:                      # the embedding's rows start the float32 stream
+                h, n = self.norm_mixer.start_forward(h)
+        elif isinstance(d, Branch):
+            n = self.norm_mixer.add_forward(h, d.tensor, post=d.norm)
+        else:
+            n = self.norm_mixer.add_forward(h, d)
+        a = Branch(self.mixer.forward(n, ctx, entry), self.post_norm_mixer)
+        if self.ffn is None:
+            return h, a
+        n = self.norm_ffn.add_forward(h, a.tensor, post=a.norm)
+        return h, Branch(self.ffn.forward(n, ctx), self.post_norm_ffn)

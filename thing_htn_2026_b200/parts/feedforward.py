@@ -1,6 +1,9 @@
 """Dense feed-forward with a gated SiLU: ``down(silu(gate(x)) * up(x))``.  Gate and up
 are one product over the concatenated weight ``[2I, H]`` (engine/engine.py:221, :1116-1118);
-the activation rounds as engine/kernels/torch_ref.py:74-88 does."""
+the activation rounds as engine/kernels/torch_ref.py:74-88 does.
+
+``clamped_glu``: ``down(g * logistic(slope * g) * (u + 1))`` with ``g = min(gate(x), limit)`` and
+``u = clamp(up(x), -limit, limit)``; ``limit`` and ``slope`` are parameters."""
 
 from __future__ import annotations
 
@@ -31,3 +34,20 @@ class SwiGLU:
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         err = getattr(ctx, "err", None)
         return ops.linear(ops.linear_swiglu(x, self.w_gate_up, err), self.w_down, err=err)
+
+
+@register_part("ffn", "clamped_glu")
+class ClampedGLU:
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
+        return SwiGLU.tensor_specs(spec)
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        self.limit, self.slope = float(spec.params["limit"]), float(spec.params["slope"])
+        self.w_gate_up = torch.cat([runtime.tensor(spec, "gate_proj"), runtime.tensor(spec, "up_proj")], dim=0).contiguous()
+        self.w_down = runtime.tensor(spec, "down_proj")
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        err = getattr(ctx, "err", None)
+        y = ops.clamped_glu(ops.linear(x, self.w_gate_up, err=err), self.limit, self.slope)
+        return ops.linear(y, self.w_down, err=err)

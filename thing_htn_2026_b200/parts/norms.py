@@ -1,10 +1,17 @@
 """RMSNorm.  ``forward`` normalises; ``add_forward`` first adds a branch's output to the
 residual stream in place (the reference fuses the two the same way,
-engine/kernels/torch_ref.py:61-68, engine/engine.py:1104-1107)."""
+engine/kernels/torch_ref.py:61-68, engine/engine.py:1104-1107).
+
+Parameters: ``size``, ``eps``; ``gain_offset`` (default 0; 1 for a gain stored around zero,
+which multiplies as ``1 + w``); ``residual`` (default: the activation type; "float32": the
+stream this norm reads is kept in float32 whatever the activation type, and every sum of the
+norm is float32 with one rounding at the output).  With a float32 stream, ``add_forward``
+also takes ``post``: another norm of this kind that the branch's output passes before it is
+added (norms on both sides of a sublayer), in the same kernel."""
 
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -19,15 +26,39 @@ from .runtime import Runtime
 class RMSNorm:
     @classmethod
     def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
-        return [TensorSpec(spec.tensors["weight"], (int(spec.params["size"]),), GAIN)]
+        init = "zero_centered" if float(spec.params.get("gain_offset", 0.0)) else None
+        return [TensorSpec(spec.tensors["weight"], (int(spec.params["size"]),), GAIN, init=init)]
 
     def __init__(self, spec: PartSpec, runtime: Runtime):
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
+        self.offset = float(spec.params.get("gain_offset", 0.0))
+        self.float32_stream = spec.params.get("residual") == "float32"
+        self.dtype = runtime.dtype
         self.gain = runtime.tensor(spec, "weight")
+        if self.float32_stream or self.offset:
+            self.as_gain = ops.Gain(self.gain.to(torch.float32).contiguous(), self.offset, self.eps)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.float32_stream or self.offset:
+            if x.dtype == torch.float32:
+                return ops.residual_norm(x, None, None, self.as_gain, self.dtype)[1]
+            # a stream that has not started yet: the rows are its first value
+            return ops.residual_norm(None, x, None, self.as_gain, self.dtype)[1]
         return ops.rmsnorm(x, self.gain, self.eps)
 
-    def add_forward(self, h: torch.Tensor, d: torch.Tensor) -> torch.Tensor:
+    def start_forward(self, x: torch.Tensor):
+        """``x`` of the activation type starts a float32 stream: returns (stream, norm of it)."""
+        return ops.residual_norm(None, x, None, self.as_gain, self.dtype)
+
+    def add_forward(self, h: torch.Tensor, d: torch.Tensor, post: Optional["RMSNorm"] = None) -> torch.Tensor:
+        if self.float32_stream:
+            return ops.residual_norm(h, d, post.as_gain if post is not None else None, self.as_gain, self.dtype)[1]
+        if post is not None or self.offset:
+            raise ops.KernelError("rmsnorm: a norm of the branch before the add, or a gain offset, needs a float32 stream")
         return ops.add_rmsnorm(h, d, self.gain, self.eps)
+
+    def add_only(self, h: torch.Tensor, d: torch.Tensor) -> None:
+        """``h <- h + self(d)`` on a float32 stream, nothing else: this norm as the one a branch
+        passes before the add, with no norm of the sum wanted."""
+        ops.residual_norm(h, d, self.as_gain, None, self.dtype)

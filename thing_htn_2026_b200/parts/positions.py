@@ -5,7 +5,12 @@ kernel that normalises q and k and writes the cache.
 the reference's expression (engine/engine.py:238-240); the device fills
 ``cos/sin[p, i]`` of ``p * inv_freq[i]`` in float32 (engine/engine.py:241-247).  The
 tables cover the longest sequence of the cache and grow on demand (the reference grows
-its tables the same way, engine/engine.py:232-251)."""
+its tables the same way, engine/engine.py:232-251).
+
+``layout`` says which entries of a head make a pair: "half" (entry i with entry
+i + rotary_dim / 2, the default) or "interleaved" (entry 2i with entry 2i + 1).
+``frequency_precision`` "float64" computes ``inv_freq`` in double precision before it is
+rounded to float32 (one rounding instead of the float32 expression's several)."""
 
 from __future__ import annotations
 
@@ -32,8 +37,15 @@ class Rope:
         self.theta = float(spec.params["theta"])
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rope: rotary_dim {self.rotary_dim} must be even and within head_dim {self.head_dim}")
-        exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).to(torch.float32) / self.rotary_dim
-        self.inv_freq = (1.0 / (self.theta ** exponent)).to(runtime.device)
+        self.layout = str(spec.params.get("layout", "half"))
+        if self.layout not in ops.ROTARY_LAYOUTS:
+            raise ValueError(f"rope: layout '{self.layout}' is not one of {sorted(ops.ROTARY_LAYOUTS)}")
+        if spec.params.get("frequency_precision") == "float64":
+            exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).to(torch.float64) / self.rotary_dim
+            self.inv_freq = (self.theta ** -exponent).to(torch.float32).to(runtime.device)
+        else:
+            exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).to(torch.float32) / self.rotary_dim
+            self.inv_freq = (1.0 / (self.theta ** exponent)).to(runtime.device)
         self.device = runtime.device
         self._tables = None
 
@@ -47,7 +59,7 @@ class Rope:
         cos = torch.empty((size, half), dtype=torch.float32, device=self.device)
         sin = torch.empty((size, half), dtype=torch.float32, device=self.device)
         ops.rope_table(cos, sin, self.inv_freq, 0, size)
-        self._tables = ops.RotaryTables(cos, sin, self.rotary_dim)
+        self._tables = ops.RotaryTables(cos, sin, self.rotary_dim, self.layout)
 
     def tables(self) -> ops.RotaryTables:
         if self._tables is None:

@@ -25,6 +25,16 @@ class Runtime:
         return self.tensors[spec.tensors[name]]
 
 
+@dataclass
+class Branch:
+    """A sublayer's output that has not been added to the residual stream yet, with the norm
+    it passes before the add (None: it is added as it is).  Blocks hand it on in place of a bare
+    tensor when the add is to be fused into the next norm."""
+
+    tensor: torch.Tensor
+    norm: Optional[object] = None
+
+
 @dataclass(frozen=True)
 class HostBatch:
     """What the host knows of a step before it runs: for each sequence its slot, the tokens

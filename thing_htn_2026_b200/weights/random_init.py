@@ -40,9 +40,30 @@ def _zeros(t, generator, matrix_std, gain_std):
     return t.zero_()
 
 
+def _zero_centered(t, generator, matrix_std, gain_std):
+    """A gain stored around zero (it multiplies as ``1 + w``)."""
+    return t.normal_(0.0, gain_std, generator=generator)
+
+
+def _conv_taps(t, generator, matrix_std, gain_std):
+    """Taps of a short convolution over time: of the order of one over the tap count."""
+    return t.normal_(0.0, 1.0, generator=generator).mul_(t.shape[-1] ** -0.5)
+
+
+def _log_rate(t, generator, matrix_std, gain_std):
+    """Logarithm of a decay rate between 1/2 and 8."""
+    return t.uniform_(0.0, 1.0, generator=generator).mul_(4.0).sub_(1.0).mul_(0.6931471805599453)
+
+
+def _unit_normal(t, generator, matrix_std, gain_std):
+    return t.normal_(0.0, 1.0, generator=generator)
+
+
 # How a tensor is drawn, by the name in ``TensorSpec.init``.  ``fill(t, generator, matrix_std,
 # gain_std)`` fills ``t`` (float32 on the CPU, the held dtype on a device) in place.
-INITIALIZERS: Dict[str, Callable] = {"normal": _normal, "one_plus_normal": _one_plus_normal, "zeros": _zeros}
+INITIALIZERS: Dict[str, Callable] = {"normal": _normal, "one_plus_normal": _one_plus_normal, "zeros": _zeros,
+                                     "zero_centered": _zero_centered, "conv_taps": _conv_taps, "log_rate": _log_rate,
+                                     "unit_normal": _unit_normal}
 # The rule of a spec that names none, by its role.
 ROLE_INIT = {MATRIX: "normal", GAIN: "one_plus_normal", TABLE: "zeros"}
 
