@@ -71,7 +71,7 @@ class Arithmetic:
 
     def linear(self, x, w):
         """w is stored [out, in] and applied as w x."""
-        return self.rb(self.rb(x) @ w.to(self.work).t())
+        return self.rb(self.rb(x) @ self.rb(w.to(self.work)).t())
 
 
 # ----------------------------------------------------------------------------- mechanisms
@@ -207,7 +207,7 @@ def residual_streams(config, w, tokens, precision=torch.float32):
     """[layers run + 1, T, W]: the stream after the embedding and after every layer."""
     ar = Arithmetic(precision)
     eps = float(config["norm"]["eps"])
-    x = w["embed"].to(ar.work)[torch.tensor(tokens, dtype=torch.long)]
+    x = ar.rb(w["embed"].to(ar.work))[torch.tensor(tokens, dtype=torch.long)]
     streams = [x]
     for index, layer in enumerate(config["layers"]):
         owner = layer.get("weights_of", index)
@@ -231,7 +231,7 @@ def logits_of_stream(config, w, x, precision=torch.float32):
     ar = Arithmetic(precision)
     n = norm_one_plus(x, w["final.norm"], float(config["norm"]["eps"]))
     if ar.round_products:
-        return ar.rb(n) @ w["head"].to(ar.work).t()        # logits keep the accumulator's precision
+        return ar.rb(n) @ ar.rb(w["head"].to(ar.work)).t()        # logits keep the accumulator's precision
     return n @ w["head"].to(ar.work).t()
 
 

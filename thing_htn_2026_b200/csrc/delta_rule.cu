@@ -58,6 +58,21 @@ __device__ __forceinline__ float conv_at(const T* __restrict__ proj_row, const T
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
+// The decay g = exp(-exp(a_log) softplus(a)).  A sequence's memory of a token far back is that
+// token's write times the product of every g since, so an error of g that leans one way grows
+// with the distance.  With float32 activations g is therefore computed in double and rounded
+// once; with bfloat16 activations in float32.
+template <typename T>
+__device__ __forceinline__ float decay_of(float a_log, float a) {
+    return expf(-expf(a_log) * softplus_f(a));
+}
+template <>
+__device__ __forceinline__ float decay_of<float>(float a_log, float a) {
+    const double z = (double)a;
+    const double sp = z > 30.0 ? z : log1p(exp(z));
+    return (float)exp(-exp((double)a_log) * sp);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) delta_prepare_kernel(
     float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vc, float* __restrict__ beta,
@@ -83,7 +98,7 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(
         const float b = to_f32<T>(row[s.b_offset() + h]);
         beta[(size_t)m * s.n_heads + h] = 1.0f / (1.0f + expf(-b));
         const float a = to_f32<T>(row[s.a_offset() + h]) + dt_bias[h];
-        decay[(size_t)m * s.n_heads + h] = expf(-expf(a_log[h]) * softplus_f(a));
+        decay[(size_t)m * s.n_heads + h] = decay_of<T>(a_log[h], a);
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -294,7 +309,7 @@ __global__ void __launch_bounds__(kRecurrenceWarps * 32) delta_decode_kernel(
         if (l == 0) ring_slot[(size_t)(pos % s.taps) * C + c] = row[c];
     }
     const float b = 1.0f / (1.0f + expf(-to_f32<T>(row[s.b_offset() + head])));
-    const float gd = expf(-expf(a_log[head]) * softplus_f(to_f32<T>(row[s.a_offset() + head]) + dt_bias[head]));
+    const float gd = decay_of<T>(a_log[head], to_f32<T>(row[s.a_offset() + head]) + dt_bias[head]);
     __syncthreads();
     float tk = 0.f, tq = 0.f;
 #pragma unroll
