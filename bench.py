@@ -19,6 +19,13 @@ configuration, batch, prompt length and step counts, and prints the same line wi
 prompts of 64 to 2,048 tokens and 128 greedy steps at the Qwen3-8B sizes; batch 64 with
 1,024-token prompts and 256 steps, half of the sequences sampling at temperature 0.8, at the
 Qwen3-14B sizes.
+
+``--design lanilix`` measures the Lanilix decoder instead (named configurations
+``lanilix-w2048`` and ``lanilix-w4096``: eight layers, three gated-delta-rule layers to one
+windowed-attention layer) beside a Qwen3 decoder of the same width, feed-forward, heads, head
+size, depth and vocabulary: prefill of one 2,048-token prompt and decode steps at ``--batch``,
+and every kernel of the new design alone (cold caches) beside the like kernel of the Qwen3
+path, each with the fraction of its roofline.  The default run is untouched by it.
 """
 
 from __future__ import annotations
@@ -433,6 +440,259 @@ def run_workload(args):
     return 0
 
 
+# ----------------------------------------------------------------------------- another design beside the closest model
+
+DESIGN_SIZES = ("lanilix-w2048", "lanilix-w4096")
+FP32_CORE_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12        # FFMA peak of the CUDA cores at the maximum clock
+
+
+def qwen3_like(lan):
+    """A Qwen3 config.json of the same width, feed-forward, heads, head size, depth and
+    vocabulary as a Lanilix configuration (its attention layer's head counts)."""
+    attn = next(l for l in lan["layers"] if l["type"] == "attention")
+    ff = next(l["mlp"]["ff"] for l in lan["layers"] if l["mlp"])
+    m = attn["mixer"]
+    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu", "attention_bias": False,
+            "rope_scaling": None, "vocab_size": lan["vocab"], "hidden_size": lan["width"], "intermediate_size": ff,
+            "num_hidden_layers": len(lan["layers"]), "num_attention_heads": m["heads"],
+            "num_key_value_heads": m["kv_heads"], "head_dim": m["dim"], "rms_norm_eps": lan["norm"]["eps"],
+            "rope_theta": 1000000.0, "tie_word_embeddings": False, "max_position_embeddings": 8192}
+
+
+def measure_model(torch, engine, vocab, batch, prompt_len, steps, warmup):
+    """Prefill of one PREFILL_TOKENS prompt (median of 5 after 3) and graph decode steps at
+    ``batch`` after ``prompt_len``-token prompts, both on the device with CUDA events."""
+    from thing_htn_2026_b200.engine.generation import Request
+    from thing_htn_2026_b200.engine.step import StepEntry
+    backend = engine.backend
+    g = torch.Generator().manual_seed(0)
+    times = []
+    for _ in range(8):
+        (slot,) = backend.cache.open(1)
+        toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        backend.runner.step([StepEntry(slot, toks, (PREFILL_TOKENS - 1,))], check=False)
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end))
+        backend.cache.close([slot])
+    prefill_ms = statistics.median(times[3:])
+    requests = [Request(torch.randint(0, vocab, (prompt_len,), generator=g).tolist(), warmup + steps + 1, 0.0, 0, i)
+                for i in range(batch)]
+    slots = backend.open_batch(requests)
+    try:
+        backend.fetch(backend.launch_prefill(slots, [r.tokens for r in requests]))
+        for _ in range(warmup):
+            backend.fetch(backend.launch_decode(slots))
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        handles = []
+        for _ in range(steps):
+            handles.append(backend.launch_decode(slots))
+            if len(handles) > 3:
+                backend.fetch(handles.pop(0))
+        end.record()
+        torch.cuda.synchronize()
+        for handle in handles:
+            backend.fetch(handle)
+        decode_ms = start.elapsed_time(end) / steps
+    finally:
+        backend.close_batch(slots)
+    return {"prefill_ms": prefill_ms, "prefill_tok_s": PREFILL_TOKENS / (prefill_ms * 1e-3),
+            "decode_ms_per_step": decode_ms, "decode_tok_s": batch * 1000.0 / decode_ms}
+
+
+def kernel_table(torch, lan, peak, batch, context):
+    """Every kernel of the new design alone, beside the like kernel of the Qwen3 path, cold
+    caches (a buffer larger than L2 is written between timed launches): microseconds, and the
+    fraction of the roofline that the kernel's algorithmic bytes or flops amount to."""
+    from thing_htn_2026_b200 import ops
+    from thing_htn_2026_b200.cache import KVSpec, SequenceCache, StateSpec
+    dev, bf = "cuda:0", torch.bfloat16
+    attn = next(l for l in lan["layers"] if l["type"] == "attention")["mixer"]
+    delta = next(l for l in lan["layers"] if l["type"] == "delta")["mixer"]
+    W, I = lan["width"], next(l["mlp"]["ff"] for l in lan["layers"] if l["mlp"])
+    H, G, D = attn["heads"], attn["kv_heads"], attn["dim"]
+    window, keep = attn["mask"]["size"], attn["mask"]["keep_first"]
+    T = PREFILL_TOKENS
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    hbm, tensor = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12
+
+    def timed(fn, reps=7):
+        out = []
+        for _ in range(reps):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            out.append(start.elapsed_time(end) * 1e3)
+        return statistics.median(out[2:])
+
+    rows = {}
+
+    def row(name, fn, nbytes=0, flops=0, flop_peak=None, like=None):
+        us = timed(fn)
+        t_roof = max(nbytes / hbm, flops / (flop_peak or tensor)) * 1e6
+        rows[name] = {"us": round(us, 2), "roofline_us": round(t_roof, 2), "frac": round(t_roof / us, 3), "like": like,
+                      "bound": "hbm" if nbytes / hbm >= flops / (flop_peak or tensor) else "flops"}
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev)
+    err = ops.new_error_word(dev)
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        # ---- norms: float32 stream with a norm on both sides of the sublayer, against add + norm in bfloat16
+        h32, d16 = rnd(n, W), rnd(n, W).to(bf)
+        gain = ops.Gain(rnd(W) * 0.1, 1.0, 1e-6)
+        h16, w16 = rnd(n, W).to(bf), (1 + rnd(W) * 0.1).to(bf)
+        row(f"{tag}: residual_norm (float32 stream, two norms)", lambda: ops.residual_norm(h32, d16, gain, gain, bf),
+            nbytes=n * W * (4 + 4 + 2 + 2), like=f"{tag}: add_rmsnorm")
+        row(f"{tag}: add_rmsnorm", lambda: ops.add_rmsnorm(h16, d16, w16, 1e-6), nbytes=n * W * (2 + 2 + 2 + 2))
+        # ---- gated units
+        gu = rnd(n, 2 * I).to(bf)
+        row(f"{tag}: clamped_glu", lambda: ops.clamped_glu(gu, 7.0, 1.702), nbytes=n * I * 6, like=f"{tag}: swiglu")
+        row(f"{tag}: swiglu", lambda: ops.swiglu(gu), nbytes=n * I * 6)
+
+    # ---- attention: one sequence of T tokens, then a decode step of `batch` sequences at `context` keys
+    def attention_rows(spec, general, tag_new, likes):
+        n_slots = batch + 1
+        cache = SequenceCache([spec], max_tokens=(batch * (context + 64) + T + 64), dtype=bf, device=dev, max_slots=n_slots + 1)
+        slots = cache.open(n_slots)
+        width = (H + (1 if general else 2) * G) * D
+        pos = ops.RotaryTables(torch.zeros(8192, D // 4 if general else D // 2, device=dev) + 1.0,
+                               torch.zeros(8192, D // 4 if general else D // 2, device=dev), D // 2 if general else D,
+                               "interleaved" if general else "half")
+        qg, kg = (1 + rnd(H * D) * 0.1, 1 + rnd(G * D) * 0.1) if general else ((1 + rnd(D) * 0.1).to(bf), (1 + rnd(D) * 0.1).to(bf))
+
+        def prepare(proj, rows_):
+            kv = cache.kv_view(0)
+            if general:
+                return ops.qk_prepare(proj, qg, kg, "projection", 1e-6, pos, rows_, kv, H, True, True, err)
+            return ops.qk_norm_rope_cache(proj, qg, kg, 1e-6, pos, rows_, kv, H, True, err)
+
+        def step_of(slot_list, counts):
+            cache.prepare(slot_list, counts)
+            cu = [0]
+            for c in counts:
+                cu.append(cu[-1] + c)
+            cu_dev = torch.tensor(cu, dtype=torch.int32, device=dev)
+            slots_dev = torch.tensor(slot_list, dtype=torch.int32, device=dev)
+            rows_ = ops.step_rows(cu_dev, slots_dev, cache.seq_lens, cu[-1], max(counts),
+                                  max_context=max(cache.length(s) + c for s, c in zip(slot_list, counts)),
+                                  lengths_differ=False)
+            return rows_, cu_dev, slots_dev
+
+        # the prompt
+        rows_, cu_dev, slots_dev = step_of([slots[0]], [T])
+        proj = rnd(T, width).to(bf)
+        size = ops.prompt_attention_tile(bf, D, cache.page_size, H, G)
+        r0, rn = ops.row_tiles_of([T], [0], size)
+        tiles = ops.RowTiles(torch.tensor(r0, dtype=torch.int32, device=dev), torch.tensor(rn, dtype=torch.int32, device=dev),
+                             len(r0), size)
+        w, k = (spec.window, spec.keep_first)
+        seen = sum(min(i + 1, (w or T) + (k if w else 0)) for i in range(T))
+        row(f"prefill: {tag_new[0]}", lambda: prepare(proj, rows_), nbytes=T * width * 2 + T * (H + 2 * G) * D * 2,
+            like=likes[0])
+        q = prepare(proj, rows_)
+        row(f"prefill: {tag_new[1]}", lambda: ops.attention(q, rows_, cache.kv_view(0), H, D ** -0.5, w, err, tiles, k),
+            flops=4.0 * H * D * seen, nbytes=T * H * D * 4, like=likes[1])
+        # the decode step: fill `batch` sequences with `context` keys first
+        others = slots[1:]
+        rows_, cu_dev, slots_dev = step_of(others, [context] * batch)
+        prepare(rnd(batch * context, width).to(bf), rows_)
+        ops.advance(cache.seq_lens, slots_dev, cu_dev)
+        cache.commit(others, [context] * batch)
+        rows_, cu_dev, slots_dev = step_of(others, [1] * batch)
+        proj1 = rnd(batch, width).to(bf)
+        row(f"decode: {tag_new[0]}", lambda: prepare(proj1, rows_), nbytes=batch * (width * 2 + (H + 2 * G) * D * 2),
+            like=likes[2])
+        q1 = prepare(proj1, rows_)
+        keys = min(context + 1, (w or context + 1) + (k if w else 0))
+        row(f"decode: {tag_new[1]}", lambda: ops.attention(q1, rows_, cache.kv_view(0), H, D ** -0.5, w, err, None, k),
+            nbytes=batch * G * keys * D * 2 * 2, like=likes[3])
+
+    attention_rows(KVSpec(G, D, None, 0), False, ("qk_norm_rope_cache", "attention (all keys)"), (None,) * 4)
+    attention_rows(KVSpec(G, D, window, keep), True, ("qk_prepare", f"attention (window {window} + {keep} kept)"),
+                   ("prefill: qk_norm_rope_cache", "prefill: attention (all keys)", "decode: qk_norm_rope_cache",
+                    "decode: attention (all keys)"))
+
+    # ---- the delta rule: a prompt of T tokens, then a step of `batch` sequences
+    shape = ops.DeltaShape(delta["heads"], delta["kv_heads"], delta["dim"], delta["vdim"], delta["conv"])
+    Hd, dk, dv = shape.n_heads, shape.key_dim, shape.value_dim
+    cache = SequenceCache([(StateSpec((Hd, dv, dk), torch.float32), StateSpec((shape.taps, shape.conv_channels), bf))],
+                          max_tokens=64 * (batch + 2), dtype=bf, device=dev, max_slots=batch + 2)
+    slots = cache.open(batch + 1)
+    conv_w, a_log, dt_bias = rnd(shape.conv_channels, shape.taps) * 0.5, rnd(Hd) - 3.0, rnd(Hd)
+    state, ring = cache.state_view(0, 0), cache.state_view(0, 1)
+    for n, who, tag in ((T, [slots[0]], "prefill"), (1, slots[1:], "decode")):
+        cu = torch.arange(len(who) + 1, dtype=torch.int32, device=dev) * n
+        slots_dev = torch.tensor(who, dtype=torch.int32, device=dev)
+        rows_ = ops.step_rows(cu, slots_dev, cache.seq_lens, n * len(who), n)
+        proj = rnd(n * len(who), shape.proj_width).to(bf)
+        tokens = n * len(who)
+        state_bytes = len(who) * Hd * dk * dv * 4 * 2
+        row(f"{tag}: delta_rule (conv, norms, recurrence)",
+            lambda: ops.delta_rule(proj, conv_w, a_log, dt_bias, state, ring, rows_, cache.seq_lens, shape, 1e-6),
+            nbytes=state_bytes + tokens * (shape.proj_width * 2 + Hd * dv * 4), flops=6.0 * tokens * Hd * dk * dv,
+            flop_peak=FP32_CORE_TFLOPS * 1e12, like=f"{tag}: attention (all keys)")
+        o = rnd(tokens, Hd, dv)
+        wn = 1 + rnd(dv) * 0.1
+        row(f"{tag}: gated_head_norm", lambda: ops.gated_head_norm(o, proj, shape.gate_offset, wn, 1e-6, Hd, dv, bf),
+            nbytes=tokens * Hd * dv * (4 + 2 + 2), like=f"{tag}: swiglu")
+    ops.raise_on_device_error(err, "kernel table")
+    for name, r in rows.items():
+        if r["like"] in rows:
+            r["times_farther_than_like"] = round(rows[r["like"]]["frac"] / r["frac"], 2)
+    return rows
+
+
+def run_design(args):
+    import torch
+    from thing_htn_2026_b200 import Engine, ops
+    from thing_htn_2026_b200.config import config_from_dict, named_config_json
+    peak = peaks()
+    warmup = max(args.warmup, 3)
+    steps = args.steps if args.steps_given else 64
+    sizes = {}
+    sampler = ClockSampler()
+    sampler.start()
+    ops.launch_count = 0
+    for name in DESIGN_SIZES:
+        lan = named_config_json(name)
+        if args.layers:
+            lan["layers"] = lan["layers"][:args.layers]
+        per_seq = -(-(args.prompt_len + warmup + steps + 2) // 64) * 64
+        max_tokens = max(args.batch * per_seq, PREFILL_TOKENS + 64) + 64
+        entry = {"layers": [l["type"] for l in lan["layers"]], "width": lan["width"]}
+        for label, data in (("lanilix", lan), ("qwen3_same_size", qwen3_like(lan))):
+            engine = Engine.from_config(config_from_dict(data), seed=0, dtype="bfloat16", max_tokens=max_tokens,
+                                        max_batch=args.batch)
+            entry[label] = measure_model(torch, engine, data.get("vocab", data.get("vocab_size")), args.batch,
+                                         args.prompt_len, steps, warmup)
+            del engine
+            torch.cuda.empty_cache()
+        entry["kernels"] = kernel_table(torch, lan, peak, args.batch, args.prompt_len)
+        sizes[name] = entry
+    clocks = sampler.stop()
+    first = sizes[DESIGN_SIZES[0]]
+    print(json.dumps({
+        "metric": f"decode tok/s at batch {args.batch} (Lanilix, {DESIGN_SIZES[0]}, random bf16 weights, 1 B200)",
+        "value": first["lanilix"]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": first["lanilix"]["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random-init weights, seeded uniform-random token ids",
+        "impl": "ours", "design": "lanilix",
+        "config": {"model": DESIGN_SIZES[0], "global_batch": args.batch, "seq_len": args.prompt_len + warmup + steps,
+                   "prompt_len": args.prompt_len, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
+                   "l2": "kernel table: a 256 MB buffer is written between timed launches", "peaks": peak["source"],
+                   "fp32_core_tflops": FP32_CORE_TFLOPS},
+        "gpu_launches": ops.launch_count, "sizes": sizes, "clocks": clocks}))
+    return 0
+
+
 # ----------------------------------------------------------------------------- the reference arm
 
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
@@ -629,6 +889,9 @@ def main():
                              "(for ncu --profile-from-start off)")
     parser.add_argument("--workload", choices=sorted(LARGE_WORKLOADS), default=None,
                         help="one of the two larger workloads instead of the default run")
+    parser.add_argument("--design", choices=["lanilix"], default=None,
+                        help="another design beside a Qwen3 decoder of the same sizes, model by model and kernel by "
+                             "kernel, instead of the default run")
     args = parser.parse_args()
     args.steps_given = args.steps is not None
     if args.steps is None:
@@ -640,6 +903,8 @@ def main():
         return run_reference(args)
     if args.workload:
         return run_workload(args)
+    if args.design:
+        return run_design(args)
     return run_ours(args)
 
 

@@ -46,10 +46,11 @@ def position_error(got, want):
 
 
 def check_logits(got, folder, tokens, dtype, what, places=None):
-    """float32: within a few float32 roundings of the plain float32 result.  bfloat16: no farther
-    from exact arithmetic than three times the plain implementation's own bfloat16 emulation is
-    (at that place, or typically over the places, whichever is more: one place's emulation
-    error can be small by chance)."""
+    """float32: within a few float32 roundings of the plain float32 result.  bfloat16, against
+    exact arithmetic and measured by the plain implementation's own bfloat16 emulation: the worst
+    place no worse than twice the emulation's worst place (single places flip roundings by
+    chance), and the mean over the places no more than one and a half times the emulation's
+    mean (a fault that touches most places moves the mean)."""
     places = list(range(len(tokens))) if places is None else places
     assert got.shape[0] == len(places), f"{what}: {got.shape[0]} rows for {len(places)} places"
     exact = oracle(folder, tokens, torch.float64)[places]
@@ -60,10 +61,12 @@ def check_logits(got, folder, tokens, dtype, what, places=None):
     else:
         noise = position_error(oracle(folder, tokens, torch.bfloat16)[places], exact)
         err = position_error(got, exact)
-        bound = 3.0 * np.maximum(noise, np.sqrt((noise * noise).mean())) + 2e-3 * spread
-        worst = int((err / bound).argmax())
-        assert (err <= bound).all(), (f"{what}: bfloat16 logits are {err[worst]:.3e} from exact at place "
-                                      f"{places[worst]}, the emulation {noise[worst]:.3e}")
+        worst = int(err.argmax())
+        assert err.max() <= 2.0 * noise.max() + 2e-3 * spread, (
+            f"{what}: bfloat16 logits are {err[worst]:.3e} from exact at place {places[worst]}, the emulation's worst "
+            f"{noise.max():.3e}")
+        assert err.mean() <= 1.5 * noise.mean() + 1e-3 * spread, (
+            f"{what}: bfloat16 logits are {err.mean():.3e} from exact on average, the emulation {noise.mean():.3e}")
 
 
 def run_trace(folder, dtype, records, tmp_path, requests, what, max_tokens=None):

@@ -68,7 +68,10 @@ def _named_config(args):
     from .config import config_from_dict, named_config_json
     data = named_config_json(args.random_config)
     if getattr(args, "layers", 0):
-        data["num_hidden_layers"] = args.layers
+        if isinstance(data.get("layers"), list):          # a configuration that lists its layers one by one
+            data["layers"] = data["layers"][:args.layers]
+        else:
+            data["num_hidden_layers"] = args.layers
     return config_from_dict(data)
 
 

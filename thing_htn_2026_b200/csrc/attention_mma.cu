@@ -16,6 +16,15 @@
 
 #include "common.cuh"
 
+// The keys a query may see besides causality: the last `size` positions (0: all), and with a
+// window also the first `keep` positions of the sequence.  Reads as the window's size where
+// only that is asked for.
+struct KeyWindow {
+    int size, keep;
+    __host__ __device__ KeyWindow(int s = 0, int k = 0) : size(s), keep(s > 0 ? k : 0) {}
+    __host__ __device__ operator int() const { return size; }
+};
+
 namespace {
 
 constexpr int kTile = 64;        // keys per tile == page size
@@ -161,7 +170,7 @@ template <int D>
 __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
     __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const int* __restrict__ tile_row0,
     const int* __restrict__ tile_rows, const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv,
-    int n_q, float scale_log2, int window, int* __restrict__ err) {
+    int n_q, float scale_log2, KeyWindow window, int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int kPitch = D + 8;
@@ -193,6 +202,11 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
     int first_key = 0;
     if (window > 0 && pos0 - window + 1 > 0) first_key = pos0 - window + 1;
     const int t_first = first_key / kTile, t_last = pos_last / kTile;
+    // Key tiles in the order they are visited: those of the kept first positions that lie before
+    // the window's first tile, then the window's.
+    const int n_kept = min((window.keep + kTile - 1) / kTile, t_first);
+    const int n_visits = n_kept + (t_last - t_first + 1);
+    auto tile_of = [&](int visit) { return visit < n_kept ? visit : t_first + (visit - n_kept); };
 
     auto issue = [&](int t, int stage) {
         const int page = pages[t];
@@ -205,7 +219,7 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
         }
         cp_async_commit();
     };
-    issue(t_first, 0);
+    issue(tile_of(0), 0);
 
     cp_async_wait<1>();          // Q has landed
     __syncthreads();
@@ -224,9 +238,10 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
     const int g = lane >> 2, tq = lane & 3;
     const int my_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};
 
-    for (int t = t_first; t <= t_last; ++t) {
-        const int stage = (t - t_first) & 1;
-        if (t < t_last) issue(t + 1, stage ^ 1); else cp_async_commit();
+    for (int visit = 0; visit < n_visits; ++visit) {
+        const int t = tile_of(visit);
+        const int stage = visit & 1;
+        if (visit + 1 < n_visits) issue(tile_of(visit + 1), stage ^ 1); else cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
         const int key0 = t * kTile;
@@ -244,7 +259,7 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
                     if (need_mask) {
                         const int key = key0 + n * 8 + tq * 2 + (i & 1);
                         const int p = my_pos[i >> 1];
-                        if (key > p || (window > 0 && key <= p - window)) v = -INFINITY;
+                        if (key > p || (window > 0 && key <= p - window && key >= window.keep)) v = -INFINITY;
                     }
                     s[n][i] = v;
                 }
@@ -359,7 +374,7 @@ template <int D, int STAGES, bool FUSED, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const __nv_bfloat16* __restrict__ q, const int* __restrict__ row_slot, const int* __restrict__ row_pos,
-    PagedKV kv, int n_q, int n_splits, float scale_log2, int window, int* __restrict__ counters,
+    PagedKV kv, int n_q, int n_splits, float scale_log2, KeyWindow window, int* __restrict__ counters,
     int* __restrict__ err, FusedInput fused) {
     pdl_launch_dependents();
     pdl_wait();
@@ -414,14 +429,19 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     int first_key = 0;
     if (window > 0 && pos - window + 1 > 0) first_key = pos - window + 1;
     const int t_first = first_key / kTile, t_last = pos / kTile;
-    const int n_tiles = t_last - t_first + 1;
+    // Key tiles are counted in the order they are visited: those of the kept first positions that
+    // lie before the window's first tile, then the window's.  t_begin, t_end and the loop below
+    // count visits; tile_of gives the tile.
+    const int n_kept = min((window.keep + kTile - 1) / kTile, t_first);
+    const int n_tiles = n_kept + t_last - t_first + 1;
+    auto tile_of = [&](int visit) { return visit < n_kept ? visit : t_first + (visit - n_kept); };
     // as even as it goes: the first n_tiles % n_splits splits take one tile more than the others
     const int per_split = n_tiles / n_splits, longer = n_tiles - per_split * n_splits;
-    const int t_begin = t_first + split * per_split + min(split, longer);
+    const int t_begin = split * per_split + min(split, longer);
     const int t_end = t_begin + per_split + (split < longer ? 1 : 0);      // exclusive; == t_begin for an empty split
 
     __nv_bfloat16 new_k_lo[E], new_k_hi[E];
-    const bool patches = FUSED && fused.write_cache && t_begin <= t_last && t_last < t_end;
+    const bool patches = FUSED && fused.write_cache && t_begin <= n_tiles - 1 && n_tiles - 1 < t_end;
     if (!FUSED) {
         for (int c = threadIdx.x; c < 16 * (D / 8); c += kThreads) {
             const int r = c / (D / 8), col = (c % (D / 8)) * 8;
@@ -435,7 +455,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
 
     // (the page of a tile is looked up a tile before its loads are issued: the loads' addresses
     // wait for it, and a lookup per tile in the loop would stall the block once per tile)
-    auto page_of = [&](int t) { return t < t_end ? pages[t] : 0; };
+    auto page_of = [&](int t) { return t < t_end ? pages[tile_of(t)] : 0; };
     auto issue = [&](int t, int stage, int page) {
         if (t < t_end) {
             if (page < 0) {
@@ -524,10 +544,10 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         issue(t + kStages - 1, stage == 0 ? kStages - 1 : stage - 1, page_now);     // into the buffer the last tile left
         cp_async_wait<kStages - 1>();
         __syncthreads();
-        if constexpr (FUSED) if (patches && t == t_last) {
+        if constexpr (FUSED) if (patches && t == n_tiles - 1) {
             // the tile came from the cache without this step's token: put it in, here and there
             if (warp == 0) {
-                const int page = pages[t], in_page = pos % kTile, d0 = lane * E;
+                const int page = pages[t_last], in_page = pos % kTile, d0 = lane * E;
                 if (page >= 0) {
                     __nv_bfloat16* k_dst = (__nv_bfloat16*)kv.base + kv_offset(kv, page, 0, kvh, in_page);
                     __nv_bfloat16* v_dst = (__nv_bfloat16*)kv.base + kv_offset(kv, page, 1, kvh, in_page);
@@ -544,7 +564,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
             }
             __syncthreads();
         }
-        const int key0 = t * kTile + warp * 16;
+        const int key0 = tile_of(t) * kTile + warp * 16;
         float s[2][4];
         qk_tile<D, 2>(s, qf, k_smem + stage * kTile * kPitch, warp * 2, lane);
 #pragma unroll
@@ -552,7 +572,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = key0 + n * 8 + tq * 2 + (i & 1);
-                const bool visible = key <= pos && key >= first_key;
+                const bool visible = key <= pos && (key >= first_key || key < window.keep);
                 s[n][i] = visible ? s[n][i] * scale_log2 : -INFINITY;
             }
         uint32_t pf[1][4];
@@ -1281,7 +1301,7 @@ template <int D, int STAGES> constexpr size_t decode_smem() { return (size_t)(16
 
 template <int D>
 int launch_prefill(void* out, const void* q, const int* tile_row0, const int* tile_rows, int n_tiles,
-                   const int* row_slot, const int* row_pos, PagedKV kv, int n_q, float scale, int window, int* err,
+                   const int* row_slot, const int* row_pos, PagedKV kv, int n_q, float scale, KeyWindow window, int* err,
                    cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
@@ -1386,7 +1406,7 @@ int decode_clusters_resident(int c) {
 
 template <int D, int STAGES, bool FUSED, bool CLUSTER>
 int launch_decode_with(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
-                       PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
+                       PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, KeyWindow window, int* counters, int* err,
                        cudaStream_t stream, const FusedInput& fused) {
     int configured = configure_decode<D, STAGES, FUSED, CLUSTER>();
     if (configured != THN_OK) return configured;
@@ -1485,7 +1505,7 @@ int launch_decode_stream(void* out, const void* q, const int* row_slot, const in
 // is still resident at once is taken: it depends on the batch only, not on the lengths.
 template <int D, bool FUSED = false>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
-                  PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
+                  PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, KeyWindow window, int* counters, int* err,
                   cudaStream_t stream, FusedInput fused = FusedInput{}, long long n_pages = 0, int hints = 1) {
 #define THN_DECODE_ARGS out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream, fused
     const int n_pairs = n_seqs * kv.n_kv;
@@ -1504,7 +1524,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     // pairs of 1,024 keys on: 4.38 against 4.76 ms per step at batch 24 with 4,096 keys).
     const bool second_pass = (long long)n_pairs > (long long)sm_count() * decode_blocks_per_sm<D, 2>();
     const bool asked_for = (hints & 2) != 0;
-    if (n_splits == 1 && n_pages > 0 && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
+    if (n_splits == 1 && n_pages > 0 && window.keep == 0 && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
         const int taken = g_decode_stream_stages >= 6
             ? launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
                                                 stream, fused, hints)
@@ -1534,7 +1554,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
 // the step are resident, else through scratch memory.
 template <int D>
 int launch_decode_lite(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
-                       PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
+                       PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, KeyWindow window, int* counters, int* err,
                        cudaStream_t stream) {
     const FusedInput fused{};
 #define THN_DECODE_ARGS out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream, fused
@@ -1584,12 +1604,15 @@ THN_API int thn_attention_prefill_tile_rows() { return kPrefillRows; }
 
 // Rows of a step that brings one or more tokens per sequence.  tile_row0[i] is the first
 // packed row of tile i, tile_rows[i] (1..thn_attention_prefill_tile_rows()) the number of its rows; the rows of a tile are
-// consecutive tokens of one sequence.  q, out [rows, n_q * head_dim] bfloat16.
+// consecutive tokens of one sequence.  q, out [rows, n_q * head_dim] bfloat16.  With a window
+// (window_size > 0) the first keep_first positions of a sequence stay visible as well.
 THN_API int thn_attention_prefill_bf16(void* out, const void* q, const int* tile_row0, const int* tile_rows,
                                        int n_tiles, const int* row_slot, const int* row_pos, const void* kv_base,
                                        const int* block_table, int bt_stride, int n_kv, int page_size, int head_dim,
-                                       int n_q, float scale, int window, int* err, cudaStream_t stream) {
-    THN_CHECK_ARG(n_tiles >= 0 && n_q > 0, "attention_prefill: bad sizes");
+                                       int n_q, float scale, int window_size, int keep_first, int* err,
+                                       cudaStream_t stream) {
+    THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && keep_first >= 0, "attention_prefill: bad sizes");
+    const KeyWindow window(window_size, keep_first);
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
                        "attention_prefill: head_dim %d, page %d, heads %d/%d not supported by the tensor-core kernel",
                        head_dim, page_size, n_q, n_kv);
@@ -1668,9 +1691,11 @@ THN_API void thn_set_decode_stream(int mode, int stages) {
 THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_slot, const int* row_pos,
                                       const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                       int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
-                                      int window, float* scratch, int* counters, long long n_pages, int hints,
-                                      int* err, cudaStream_t stream) {
-    THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode: bad sizes");
+                                      int window_size, int keep_first, float* scratch, int* counters, long long n_pages,
+                                      int hints, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535 && keep_first >= 0,
+                  "attention_decode: bad sizes");
+    const KeyWindow window(window_size, keep_first);
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode: at most 32 splits with counters, got %d",
                   n_splits);
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
@@ -1784,6 +1809,6 @@ THN_API int thn_attention_decode_bf16_no_alloc(void* out, const void* q, const i
         if (scratch == nullptr) return THN_BAD_ARGUMENT;
     }
     return thn_attention_decode_bf16(out, q, row_slot, row_pos, kv_base, block_table, bt_stride, n_kv, page_size,
-                                     head_dim, n_seqs, n_q, n_splits, scale, window, scratch, nullptr, /*n_pages=*/0, /*hints=*/1, err,
+                                     head_dim, n_seqs, n_q, n_splits, scale, window, /*keep_first=*/0, scratch, nullptr, /*n_pages=*/0, /*hints=*/1, err,
                                      stream);
 }

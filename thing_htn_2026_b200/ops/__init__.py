@@ -81,9 +81,9 @@ _SIGNATURES = {
     "thn_attention_mma_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_fused_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_int,
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int,
                                   c_void_p, c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
     "thn_attention_decode_cluster_splits": [],
@@ -661,16 +661,16 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
     own keys).  Chooses the kernel by dtype, head size and step shape; the tensor-core
     kernels for steps of several tokens per sequence need ``tiles``.  With a window,
     ``keep_first`` keys at the start of a sequence stay visible to every later row."""
-    if window and keep_first:
-        return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first)
+    keep_first = int(keep_first or 0) if window else 0
     if q.dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
         if rows.max_q_len == 1:
-            return attention_decode_bf16(q, rows, kv, n_q, scale, window, err)
+            return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first)
         if tiles is not None:
-            if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
+            if (USE_TCGEN05_ATTENTION and not keep_first
+                    and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv)):
                 return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err)
-            return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err)
-    return attention_generic(q, rows, kv, n_q, scale, window, err)
+            return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first)
+    return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first)
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
@@ -703,7 +703,7 @@ def _check_tiles(tiles: RowTiles) -> None:
 
 
 def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
-                           window: Optional[int], err: torch.Tensor) -> torch.Tensor:
+                           window: Optional[int], err: torch.Tensor, keep_first: int = 0) -> torch.Tensor:
     """Tensor-core flash attention for steps with several tokens per sequence."""
     _need(q, "attention q", torch.bfloat16)
     out = torch.empty_like(q)
@@ -711,7 +711,7 @@ def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv:
     _call("thn_attention_prefill_bf16", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
           tiles.n, _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
           kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale), int(window or 0),
-          _ptr(err), _stream())
+          int(keep_first or 0), _ptr(err), _stream())
     return out
 
 
@@ -773,7 +773,8 @@ def decode_hints(rows: StepRows, n_kv: int, n_splits: int, device) -> int:
 
 def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
                           window: Optional[int], err: torch.Tensor, n_splits: Optional[int] = None,
-                          scratch: Optional[torch.Tensor] = None, fused_merge: bool = True) -> torch.Tensor:
+                          scratch: Optional[torch.Tensor] = None, fused_merge: bool = True,
+                          keep_first: int = 0) -> torch.Tensor:
     """Split-KV flash decoding: one token per sequence.  Partial results of the splits go
     through float32 scratch memory, which is allocated here unless given."""
     _need(q, "attention q", torch.bfloat16)
@@ -790,8 +791,8 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     out = torch.empty_like(q)
     _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
-          n_seqs, n_q, n_splits, float(scale), int(window or 0), _ptr(scratch), _ptr(counters), kv.storage.shape[0],
-          decode_hints(rows, kv.n_kv, n_splits, q.device), _ptr(err), _stream())
+          n_seqs, n_q, n_splits, float(scale), int(window or 0), int(keep_first or 0), _ptr(scratch), _ptr(counters),
+          kv.storage.shape[0], decode_hints(rows, kv.n_kv, n_splits, q.device), _ptr(err), _stream())
     return out
 
 
