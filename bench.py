@@ -642,7 +642,7 @@ def kernel_table(torch, lan, peak, batch, context):
         o = rnd(tokens, Hd, dv)
         wn = 1 + rnd(dv) * 0.1
         row(f"{tag}: gated_head_norm", lambda: ops.gated_head_norm(o, proj, shape.gate_offset, wn, 1e-6, Hd, dv, bf),
-            nbytes=tokens * Hd * dv * (4 + 2 + 2), like=f"{tag}: swiglu")
+            nbytes=tokens * Hd * dv * (4 + 2 + 2), like=f"{tag}: add_rmsnorm")
     ops.raise_on_device_error(err, "kernel table")
     for name, r in rows.items():
         if r["like"] in rows:

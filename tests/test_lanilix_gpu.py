@@ -255,6 +255,30 @@ def test_mixer_alone_whole_in_portions_and_token_by_token(models, dtype, name, l
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("lanes", [8, 32])
+@pytest.mark.parametrize("name, layer", [m for m in MIXERS if tiny.CONFIGS[m[0]]["layers"][m[1]]["type"] == "delta"])
+def test_recurrence_with_either_lane_layout(models, monkeypatch, dtype, lanes, name, layer):
+    """The prompt kernel of the delta rule holds a column of the state in 8 or in 32 lanes,
+    chosen by the step's size; both are run here on the same rows, two sequences of unequal
+    lengths in one step, the longer one continued in a second step."""
+    from thing_htn_2026_b200 import ops
+    monkeypatch.setattr(ops, "DELTA_LANES", lanes)
+    folder = models[name]
+    part, config = part_of(folder, layer, "mixer", dtype)
+    data = tiny.config_json(name)["layers"][layer]
+    _, w = plain.read_model(folder)
+    xs = [rand((n, config.width), 300 + n).to(TORCH[dtype]) for n in (77, 18)]
+    ar = plain.Arithmetic(torch.float32 if dtype == "float32" else torch.bfloat16)
+    want = [plain.delta_mixer(x.float(), w, f"l{layer}.mix.", data["mixer"], config.norm_eps, ar) for x in xs]
+    stepper = Stepper(part, dtype)
+    a, b = stepper.cache.open(2)
+    first = stepper.step([a, b], [xs[0][:40], xs[1]])
+    (rest,) = stepper.step([a], [xs[0][40:]])
+    close(torch.cat([first[0], rest]), want[0], dtype, f"{lanes} lanes, two steps")
+    close(first[1], want[1], dtype, f"{lanes} lanes, beside it")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_feed_forward_alone(models, dtype):
     folder = models["q"]
     part, config = part_of(folder, 2, "ffn", dtype)

@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
     __nv_bfloat16* __restrict__ out, const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, const int* __restrict__ block_table,
-    int bt_stride, int n_kv, int n_q, float scale_log2, int window, int* __restrict__ err) {
+    int bt_stride, int n_kv, int n_q, float scale_log2, int window, int keep_first, int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];      // swizzled tiles want 1024-byte alignment
@@ -236,6 +236,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     int first_key = 0;
     if (window > 0 && pos0 - window + 1 > 0) first_key = pos0 - window + 1;
     const int t_first = first_key / kKeys, t_last = pos_last / kKeys;
+    // Key tiles in the order they are visited: those of the kept first positions that lie before
+    // the window's first tile, then the window's.  Every role below counts visits.
+    const int n_kept = window > 0 ? min((keep_first + kKeys - 1) / kKeys, t_first) : 0;
+    const int n_visits = n_kept + t_last - t_first + 1;
+    auto tile_of = [&](int visit) { return visit < n_kept ? visit : t_first + (visit - n_kept); };
     const int* pages = block_table + (size_t)row_slot[row0] * bt_stride;
 
     if (threadIdx.x == 0) {
@@ -273,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         // K pages and V pages have rings of their own: a K page is free again once S = Q K^T has
         // read it, long before the tile's V page, so K runs one tile further ahead: K(0), K(1),
         // V(0), K(2), V(1), ...
-        const int n_it = g_test_skip_kv_loads ? 0 : t_last - t_first + 1;
+        const int n_it = g_test_skip_kv_loads ? 0 : n_visits;
         auto load = [&](int it, int which) {        // which: 0 = K, 1 = V
             const int s = it % kStages;
             uint64_t* empty = which ? v_empty : k_empty;
@@ -282,7 +287,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                 if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
                 return false;
             }
-            const int page = pages[t_first + it];
+            const int page = pages[tile_of(it)];
             if (page < 0) {
                 if (err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
                 return false;
@@ -304,7 +309,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         // ---- MMA issuer.  S of tile it + 1 is multiplied while the softmax warps work on
         // tile it; O += P V of tile it follows as soon as its P is ready.
         bool ok = mbar_wait_spin(q_full, 0);
-        const int n_it = t_last - t_first + 1;
+        const int n_it = n_visits;
         const uint32_t q_addr = smem_addr(q_smem);
         auto qk = [&](int it) {          // S[it & 1] = Q K(it)^T
             const int s = it % kStages;
@@ -359,7 +364,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         float run_max = -INFINITY, run_sum = 0.f;
         bool ok = true;
         int it = 0;
-        for (int t = t_first; t <= t_last && !*give_up; ++t, ++it) {
+        for (; it < n_visits && !*give_up; ++it) {
+            const int t = tile_of(it);
             ok = mbar_wait(s_full + (it & 1), (it >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);        // the lanes leave a wait one by one; tcgen05.ld wants the warp together
             if (!ok) break;
@@ -383,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     const int key = key0 + i;
-                    const bool visible = key <= pos && (window <= 0 || key > pos - window);
+                    const bool visible = key <= pos && (window <= 0 || key > pos - window || key < keep_first);
                     s[i] = visible ? s[i] : -INFINITY;
                 }
             }
@@ -535,12 +541,14 @@ THN_API int thn_attention_tcgen05_supported(int head_dim, int page_size, int n_q
 
 // Same contract as thn_attention_prefill_bf16 with row tiles of 128 rows (tile_rows 1..128);
 // n_rows_total is the number of packed rows of q and out, n_pages the pages of the cache entry.
+// With a window the first keep_first positions of a sequence stay visible as well.
 THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* tile_row0, const int* tile_rows,
                                           int n_tiles, int n_rows_total, const int* row_slot, const int* row_pos,
                                           const void* kv_base, long long n_pages, const int* block_table,
                                           int bt_stride, int n_kv, int page_size, int head_dim, int n_q, float scale,
-                                          int window, int* err, cudaStream_t stream) {
-    THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && n_rows_total >= 0 && n_pages > 0, "attention_tcgen05: bad sizes");
+                                          int window, int keep_first, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && n_rows_total >= 0 && n_pages > 0 && keep_first >= 0,
+                  "attention_tcgen05: bad sizes");
     THN_UNSUPPORTED_IF(!thn_attention_tcgen05_supported(head_dim, page_size, n_q, n_kv),
                        "attention_tcgen05: head_dim %d, page %d, heads %d/%d not supported", head_dim, page_size, n_q,
                        n_kv);
@@ -567,6 +575,7 @@ THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* t
     }
     dim3 grid(n_q, n_tiles);
     thn_launch(attention_tcgen05_kernel, grid, kThreads, kSmemBytes, stream, map_q, map_kv, (__nv_bfloat16*)out,
-               tile_row0, tile_rows, row_slot, row_pos, block_table, bt_stride, n_kv, n_q, scale * kLog2e, window, err);
+               tile_row0, tile_rows, row_slot, row_pos, block_table, bt_stride, n_kv, n_q, scale * kLog2e, window,
+               window > 0 ? keep_first : 0, err);
     return thn_launch_status("attention_tcgen05");
 }

@@ -83,6 +83,23 @@ inline void thn_launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
     cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);   // the caller reads cudaGetLastError
 }
 
+// A launch in plain stream order, whatever the switch says: for kernels whose time is set by how
+// evenly their blocks are spread over the SMs.  Blocks of a kernel that is scheduled while its
+// predecessor still runs go wherever that one leaves room, several to an SM; a kernel with
+// about a block per SM and a long chain of dependent steps in each then takes twice as long.
+template <typename... Params, typename... Args>
+inline void thn_launch_ordered(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    config.attrs = nullptr;
+    config.numAttrs = 0;
+    cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);   // the caller reads cudaGetLastError
+}
+
 // The same with the blocks grouped into thread-block clusters of the given shape.
 template <typename... Params, typename... Args>
 inline void thn_launch_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -136,32 +136,104 @@ __device__ __forceinline__ A column_sum(A v) {
     return v;
 }
 
-// One block: one sequence of the step, one head, kColumnsPerBlock columns of its state.
-// R registers of state per lane: dk <= 8 R (entries beyond dk are zero and stay zero).
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+constexpr int kTokensPerStage = 16;
+
+// Entry of the key axis that register r of lane l (of a column's L lanes) holds.
+template <int VEC, int L>
+__device__ __forceinline__ int key_index_of(int r, int l) {
+    return VEC * (L * (r / VEC) + l) + (r % VEC);
+}
+
+template <int L, typename A>
+__device__ __forceinline__ A lanes_sum(A v) {
+#pragma unroll
+    for (int o = 1; o < L; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// One block: one sequence of the step, one head, (32 / L) * W columns of its state, a column
+// held by L lanes with R registers each (dk <= L R; entries beyond dk are zero and stay zero).
+// L = 8 does the least work per column; L = 32 gives four times as many warps with a quarter
+// of the registers each, for steps with so few columns that the schedulers would otherwise
+// have one warp each and every latency of the token-by-token chain would show.
+// The tokens' k, q, v, b and g come through shared memory, kTokensPerStage tokens at a time in
+// two buffers filled by asynchronous copies, so that every warp of the block reads one copy
+// and the next tokens travel while these are worked on; the read-outs of a stage are written
+// together.  The sums over the key axis run in up to four partial sums (a shorter chain of
+// dependent additions), in an order fixed by the lane layout.
 // A: the type the state is carried in between the step's first and last token (the state in
 // memory is float32 either way).  With double, the roundings of a long prompt's tokens do not
 // add up: the true 32-bit path uses it, so that its result is the float32 rounding of the
 // recurrence rather than a thousand roundings later.
-template <int R, int VEC, typename A>
-__global__ void __launch_bounds__(kRecurrenceWarps * 32) delta_recurrence_kernel(
+template <int R, int VEC, int L, int W, typename A>
+__global__ void __launch_bounds__(W * 32) delta_recurrence_kernel(
     float* __restrict__ o, float* __restrict__ state, const float* __restrict__ qn, const float* __restrict__ kn,
     const float* __restrict__ vc, const float* __restrict__ beta, const float* __restrict__ decay,
     const int* __restrict__ cu_seqlens, const int* __restrict__ slots, DeltaShape s) {
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int kThreads = W * 32, kTok = kTokensPerStage, kPad = L * R, kCols = (32 / L) * W;
+    constexpr int kParts = R < 4 ? R : 4;
+    // per buffer: k [kTok][kPad], q [kTok][kPad], v [kTok][kCols], b [kTok], g [kTok]; then o [kTok][kCols]
+    extern __shared__ __align__(16) float stage_mem[];
+    constexpr int kStageFloats = 2 * kTok * kPad + kTok * kCols + 2 * kTok;
+    float* o_s = stage_mem + 2 * kStageFloats;
     const int seq = blockIdx.x, head = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int l = lane & (kLanesPerColumn - 1);
-    const int col = blockIdx.z * kColumnsPerBlock + warp * kColumnsPerWarp + lane / kLanesPerColumn;
+    const int l = lane & (L - 1);
+    const int col_in_block = warp * (32 / L) + lane / L;
+    const int col0 = blockIdx.z * kCols, col = col0 + col_in_block;
     const bool live = col < s.dv;
+    const int n_cols = min(kCols, s.dv - col0);
     const int g = head / (s.n_heads / s.n_kv);
     const int row0 = cu_seqlens[seq], row1 = cu_seqlens[seq + 1];
     float* S = state + (((size_t)slots[seq] * s.n_heads + head) * s.dv + (live ? col : 0)) * s.dk;
+    const bool wide_k = s.dk % 4 == 0;
+    const bool wide_v = n_cols == kCols && s.dv % 4 == 0 && kCols % 4 == 0;
+
+    // the padding of the k and q rows stays zero for the whole kernel
+    for (int i = threadIdx.x; i < 2 * kStageFloats; i += kThreads) stage_mem[i] = 0.f;
+    __syncthreads();
+
+    auto copy16 = [](float* dst, const float* src) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+    };
+    auto copy4 = [](float* dst, const float* src) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+    };
+    // every thread takes its share of the stage's copies
+    auto issue = [&](int first_row, float* buf) {
+        const int n = min(kTok, row1 - first_row);
+        const int per_row = wide_k ? s.dk / 4 : s.dk;                 // copies per row of k or q
+        for (int e = threadIdx.x; e < 2 * n * per_row; e += kThreads) {
+            const int t2 = e / per_row, i = (e - t2 * per_row) * (wide_k ? 4 : 1);
+            const int t = t2 >> 1, is_q = t2 & 1;
+            const float* src = (is_q ? qn : kn) + ((size_t)(first_row + t) * s.n_kv + g) * s.dk + i;
+            float* dst = buf + (is_q * kTok + t) * kPad + i;
+            if (wide_k) copy16(dst, src); else copy4(dst, src);
+        }
+        float* v_s = buf + 2 * kTok * kPad;
+        const int per_v = wide_v ? kCols / 4 : n_cols;
+        for (int e = threadIdx.x; e < n * per_v; e += kThreads) {
+            const int t = e / per_v, c = (e - t * per_v) * (wide_v ? 4 : 1);
+            const float* src = vc + ((size_t)(first_row + t) * s.n_heads + head) * s.dv + col0 + c;
+            if (wide_v) copy16(v_s + t * kCols + c, src); else copy4(v_s + t * kCols + c, src);
+        }
+        float* bg_s = v_s + kTok * kCols;
+        for (int t = threadIdx.x; t < 2 * n; t += kThreads) {
+            const int tt = t < n ? t : t - n;
+            copy4(bg_s + (t < n ? 0 : kTok) + tt, (t < n ? beta : decay) + (size_t)(first_row + tt) * s.n_heads + head);
+        }
+        copy_async_commit();
+    };
 
     A st[R];
 #pragma unroll
     for (int r = 0; r < R; r += VEC) {
-        const int i = key_index<VEC>(r, l);
+        const int i = key_index_of<VEC, L>(r, l);
         if (VEC == 4) {
             const float4 v = (live && i < s.dk) ? *reinterpret_cast<const float4*>(S + i) : make_float4(0, 0, 0, 0);
             st[r] = v.x; st[r + 1] = v.y; st[r + 2] = v.z; st[r + 3] = v.w;
@@ -169,52 +241,68 @@ __global__ void __launch_bounds__(kRecurrenceWarps * 32) delta_recurrence_kernel
             st[r] = (live && i < s.dk) ? S[i] : 0.f;
         }
     }
-    float kq[2][2][R];      // [buffer][k or q][register]
-    float scal[2][3];       // v, beta, decay
-    auto fetch = [&](int m, int buf) {
-        const float* kr = kn + ((size_t)m * s.n_kv + g) * s.dk;
-        const float* qr = qn + ((size_t)m * s.n_kv + g) * s.dk;
+
+    if (row0 < row1) issue(row0, stage_mem);
+    int which = 0;
+    for (int first = row0; first < row1; first += kTok, which ^= 1) {
+        float* buf = stage_mem + which * kStageFloats;
+        if (first + kTok < row1) issue(first + kTok, stage_mem + (which ^ 1) * kStageFloats);
+        else copy_async_commit();
+        copy_async_wait<1>();
+        __syncthreads();
+        const int n = min(kTok, row1 - first);
+        const float* v_s = buf + 2 * kTok * kPad;
+        const float* bg_s = v_s + kTok * kCols;
+#pragma unroll 2
+        for (int t = 0; t < n; ++t) {
+            float kr[R], qr[R];
 #pragma unroll
-        for (int r = 0; r < R; r += VEC) {
-            const int i = key_index<VEC>(r, l);
-            if (VEC == 4) {
-                const bool in = i < s.dk;
-                const float4 a = in ? *reinterpret_cast<const float4*>(kr + i) : make_float4(0, 0, 0, 0);
-                const float4 b = in ? *reinterpret_cast<const float4*>(qr + i) : make_float4(0, 0, 0, 0);
-                kq[buf][0][r] = a.x; kq[buf][0][r + 1] = a.y; kq[buf][0][r + 2] = a.z; kq[buf][0][r + 3] = a.w;
-                kq[buf][1][r] = b.x; kq[buf][1][r + 1] = b.y; kq[buf][1][r + 2] = b.z; kq[buf][1][r + 3] = b.w;
-            } else {
-                kq[buf][0][r] = i < s.dk ? kr[i] : 0.f;
-                kq[buf][1][r] = i < s.dk ? qr[i] : 0.f;
+            for (int r = 0; r < R; r += VEC) {
+                const int i = key_index_of<VEC, L>(r, l);    // < L R: inside the padded row
+                if (VEC == 4) {
+                    const float4 a = *reinterpret_cast<const float4*>(buf + t * kPad + i);
+                    const float4 b = *reinterpret_cast<const float4*>(buf + (kTok + t) * kPad + i);
+                    kr[r] = a.x; kr[r + 1] = a.y; kr[r + 2] = a.z; kr[r + 3] = a.w;
+                    qr[r] = b.x; qr[r + 1] = b.y; qr[r + 2] = b.z; qr[r + 3] = b.w;
+                } else {
+                    kr[r] = buf[t * kPad + i];
+                    qr[r] = buf[(kTok + t) * kPad + i];
+                }
             }
-        }
-        scal[buf][0] = live ? vc[((size_t)m * s.n_heads + head) * s.dv + col] : 0.f;
-        scal[buf][1] = beta[(size_t)m * s.n_heads + head];
-        scal[buf][2] = decay[(size_t)m * s.n_heads + head];
-    };
-    if (row0 < row1) fetch(row0, 0);
-    for (int m = row0; m < row1; ++m) {
-        const int buf = (m - row0) & 1;
-        if (m + 1 < row1) fetch(m + 1, buf ^ 1);
-        const A v = scal[buf][0], b = scal[buf][1], gd = scal[buf][2];
-        A dot = 0;
+            const A v = v_s[t * kCols + col_in_block], b = bg_s[t], gd = bg_s[kTok + t];
+            A part[kParts];
 #pragma unroll
-        for (int r = 0; r < R; ++r) dot = fma(st[r], (A)kq[buf][0][r], dot);
-        dot = column_sum(dot);
-        const A u = b * (v - gd * dot);
-        A read = 0;
+            for (int i = 0; i < kParts; ++i) part[i] = 0;
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            st[r] = fma((A)kq[buf][0][r], u, gd * st[r]);
-            read = fma(st[r], (A)kq[buf][1][r], read);
+            for (int r = 0; r < R; ++r) part[r % kParts] = fma(st[r], (A)kr[r], part[r % kParts]);
+#pragma unroll
+            for (int i = 1; i < kParts; ++i) part[0] += part[i];
+            const A dot = lanes_sum<L>(part[0]);
+            const A u = b * (v - gd * dot);
+            A read[kParts];
+#pragma unroll
+            for (int i = 0; i < kParts; ++i) read[i] = 0;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                st[r] = fma((A)kr[r], u, gd * st[r]);
+                read[r % kParts] = fma(st[r], (A)qr[r], read[r % kParts]);
+            }
+#pragma unroll
+            for (int i = 1; i < kParts; ++i) read[0] += read[i];
+            const A out = lanes_sum<L>(read[0]);
+            if (l == 0) o_s[t * kCols + col_in_block] = (float)out;
         }
-        read = column_sum(read);
-        if (live && l == 0) o[((size_t)m * s.n_heads + head) * s.dv + col] = (float)read;
+        __syncthreads();
+        for (int e = threadIdx.x; e < n * n_cols; e += kThreads) {
+            const int t = e / n_cols, c = e % n_cols;
+            o[((size_t)(first + t) * s.n_heads + head) * s.dv + col0 + c] = o_s[t * kCols + c];
+        }
     }
+    copy_async_wait<0>();
     if (live) {
 #pragma unroll
         for (int r = 0; r < R; r += VEC) {
-            const int i = key_index<VEC>(r, l);
+            const int i = key_index_of<VEC, L>(r, l);
             if (i >= s.dk) continue;
             if (VEC == 4)
                 *reinterpret_cast<float4*>(S + i) = make_float4((float)st[r], (float)st[r + 1], (float)st[r + 2], (float)st[r + 3]);
@@ -222,6 +310,12 @@ __global__ void __launch_bounds__(kRecurrenceWarps * 32) delta_recurrence_kernel
                 S[i] = (float)st[r];
         }
     }
+}
+
+template <int R, int L, int W>
+constexpr size_t recurrence_smem() {
+    return sizeof(float) * (2 * (2 * kTokensPerStage * L * R + kTokensPerStage * (32 / L) * W + 2 * kTokensPerStage) +
+                            kTokensPerStage * (32 / L) * W);
 }
 
 // After a step: the raw projections of the step's last taps - 1 positions go into the ring
@@ -356,17 +450,26 @@ int check_shape(const DeltaShape& s, const char* what) {
     return THN_OK;
 }
 
-template <int R, int VEC>
+// (Launched in plain stream order: see thn_launch_ordered.  1.46 against 0.73 ms for one
+// 2,048-token prompt of 16 heads of 128 x 128 on B200.)
+template <int R, int VEC, int L, int W>
 void launch_recurrence(float* o, float* state, const float* qn, const float* kn, const float* vc, const float* beta,
                        const float* decay, const int* cu, const int* slots, int n_seqs, DeltaShape s, int carry_double,
                        cudaStream_t stream) {
-    dim3 grid(n_seqs, s.n_heads, (s.dv + kColumnsPerBlock - 1) / kColumnsPerBlock);
-    if (carry_double)
-        thn_launch(delta_recurrence_kernel<R, VEC, double>, grid, kRecurrenceWarps * 32, 0, stream, o, state, qn, kn, vc,
-                   beta, decay, cu, slots, s);
-    else
-        thn_launch(delta_recurrence_kernel<R, VEC, float>, grid, kRecurrenceWarps * 32, 0, stream, o, state, qn, kn, vc,
-                   beta, decay, cu, slots, s);
+    constexpr int kCols = (32 / L) * W;
+    constexpr size_t smem = recurrence_smem<R, L, W>();
+    dim3 grid(n_seqs, s.n_heads, (s.dv + kCols - 1) / kCols);
+    if (carry_double) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(delta_recurrence_kernel<R, VEC, L, W, double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        thn_launch_ordered(delta_recurrence_kernel<R, VEC, L, W, double>, grid, W * 32, smem, stream, o, state, qn, kn, vc, beta,
+                   decay, cu, slots, s);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(delta_recurrence_kernel<R, VEC, L, W, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        thn_launch_ordered(delta_recurrence_kernel<R, VEC, L, W, float>, grid, W * 32, smem, stream, o, state, qn, kn, vc, beta,
+                   decay, cu, slots, s);
+    }
 }
 
 template <typename T, int R, int VEC>
@@ -418,18 +521,39 @@ THN_API int thn_delta_prepare(float* qn, float* kn, float* vc, float* beta, floa
 
 // The recurrence over the rows of each of the step's sequences; o float32 [n_rows, heads, dv];
 // state float32 [slots, heads, dv, dk], read and written.  carry_double: the state is carried
-// in double between the step's first and last token.
+// in double between the step's first and last token.  lanes: 8 or 32 lanes per column of the
+// state, or 0 to choose by the step's size (the result differs by rounding only).
 THN_API int thn_delta_recurrence(float* o, float* state, const float* qn, const float* kn, const float* vc,
                                  const float* beta, const float* decay, const int* cu_seqlens, const int* slots,
-                                 int n_seqs, int n_heads, int n_kv, int dk, int dv, int carry_double,
+                                 int n_seqs, int n_heads, int n_kv, int dk, int dv, int carry_double, int lanes,
                                  cudaStream_t stream) {
     DeltaShape s{n_heads, n_kv, dk, dv, 1, 1 << 30};
     if (int status = check_shape(s, "delta_recurrence")) return status;
     if (n_seqs <= 0) return THN_OK;
     THN_UNSUPPORTED_IF(n_heads > 65535, "delta_recurrence: %d heads exceed the grid limit", n_heads);
-#define CALL(R, VEC) launch_recurrence<R, VEC>(o, state, qn, kn, vc, beta, decay, cu_seqlens, slots, n_seqs, s, carry_double, stream)
-    THN_DELTA_DISPATCH(CALL);
-#undef CALL
+    // Eight lanes per column unless that leaves most SMs without a warp; then 32 lanes.  (One
+    // 2,048-token prompt of 16 heads of 128 x 128, four warps per SM at 8 lanes: 0.65 ms against
+    // 0.72 ms with 32 lanes, which execute twice the instructions.)
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    const long long warps_at_8 = (long long)n_seqs * n_heads * dv / 4;
+    const bool narrow = lanes > 0 ? lanes == 8 : warps_at_8 >= (long long)(sms > 0 ? sms : 148) * 2;
+    const bool vec = dk % 4 == 0;
+#define CALL8(R, VEC) launch_recurrence<R, VEC, 8, 4>(o, state, qn, kn, vc, beta, decay, cu_seqlens, slots, n_seqs, s, carry_double, stream)
+#define CALL32(R, VEC) launch_recurrence<R, VEC, 32, 8>(o, state, qn, kn, vc, beta, decay, cu_seqlens, slots, n_seqs, s, carry_double, stream)
+    if (narrow) {
+        THN_DELTA_DISPATCH(CALL8);
+    } else if (dk <= 32) {
+        CALL32(1, 1);
+    } else if (dk <= 64) {
+        CALL32(2, 1);
+    } else if (dk <= 128) {
+        if (vec) CALL32(4, 4); else CALL32(4, 1);
+    } else {
+        if (vec) CALL32(8, 4); else CALL32(8, 1);
+    }
+#undef CALL8
+#undef CALL32
     return thn_launch_status("delta_recurrence");
 }
 

@@ -68,7 +68,7 @@ _SIGNATURES = {
                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_float, c_int, c_void_p],
     "thn_delta_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                             c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "thn_delta_conv_ring_update": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_int, c_int, c_void_p],
     "thn_delta_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -95,7 +95,7 @@ _SIGNATURES = {
     "thn_attention_tcgen05_test_skip_loads": [c_int],
     "thn_attention_prefill_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                      c_int, c_void_p, c_void_p],
+                                      c_int, c_int, c_void_p, c_void_p],
 }
 
 _lib = None
@@ -666,15 +666,14 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
         if rows.max_q_len == 1:
             return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first)
         if tiles is not None:
-            if (USE_TCGEN05_ATTENTION and not keep_first
-                    and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv)):
-                return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err)
+            if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
+                return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first)
             return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first)
     return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first)
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
-                              window: Optional[int], err: torch.Tensor) -> torch.Tensor:
+                              window: Optional[int], err: torch.Tensor, keep_first: int = 0) -> torch.Tensor:
     """tcgen05 / TMEM / TMA flash attention for steps with several tokens per sequence
     (bfloat16, head size 128)."""
     _need(q, "attention q", torch.bfloat16)
@@ -683,7 +682,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, 
     _call("thn_attention_prefill_tcgen05", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
           tiles.n, q.shape[0], _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), kv.storage.shape[0],
           _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale),
-          int(window or 0), _ptr(err), _stream())
+          int(window or 0), int(keep_first or 0), _ptr(err), _stream())
     return out
 
 
@@ -877,6 +876,7 @@ def _delta_check(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, 
                           f"{tuple(state.shape)}, ring {tuple(ring.shape)} do not fit {shape}")
 
 
+DELTA_LANES = int(os.environ.get("THN_DELTA_LANES", 0))     # 8 or 32 lanes per state column; 0: by the step's size
 FUSE_DELTA_DECODE = os.environ.get("THN_FUSE_DELTA_DECODE", "1").strip().lower() not in ("0", "false", "no", "off")
 
 
@@ -914,7 +914,7 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt
           s.n_heads, s.n_kv, s.key_dim, s.value_dim, s.taps, s.proj_width, float(unit_eps), code, _stream())
     _call("thn_delta_recurrence", _ptr(o), _ptr(state), _ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(decay),
           _ptr(rows.cu_seqlens), _ptr(rows.slots), rows.n_seqs, s.n_heads, s.n_kv, s.key_dim, s.value_dim,
-          int(proj.dtype == torch.float32), _stream())
+          int(proj.dtype == torch.float32), DELTA_LANES, _stream())
     _call("thn_delta_conv_ring_update", _ptr(ring), _ptr(proj), _ptr(rows.cu_seqlens), _ptr(rows.slots), _ptr(seq_lens),
           rows.n_seqs, s.n_heads, s.n_kv, s.key_dim, s.value_dim, s.taps, s.proj_width, code, _stream())
     return o
