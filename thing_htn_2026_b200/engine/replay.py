@@ -24,16 +24,21 @@ from typing import Dict
 
 import torch
 
-from ..cache.sequence_cache import SequenceCache
+from ..cache.sequence_cache import PAGE_SIZE, SequenceCache
 from .loading import load_model, parse_dtype
 from .step import StepEntry, StepRunner
+
+
+SLACK_REQUESTS = 64     # live requests whose last, partly filled page the pool has room for beyond --max-tokens
 
 
 class Replayer:
     def __init__(self, model_dir: str, dtype, max_tokens: int, out_dir: str, device: str = "cuda:0"):
         self.model = load_model(model_dir, dtype, device)
-        self.cache = SequenceCache(self.model.cache_needs(), max_tokens=max_tokens, dtype=parse_dtype(dtype),
-                                   device=device)
+        # The pool is counted in whole pages per live request; ``max_tokens`` may have been
+        # counted in tokens.  A page of slack for each of SLACK_REQUESTS live requests covers it.
+        self.cache = SequenceCache(self.model.cache_needs(), max_tokens=int(max_tokens) + SLACK_REQUESTS * PAGE_SIZE,
+                                   dtype=parse_dtype(dtype), device=device)
         self.runner = StepRunner(self.model, self.cache)
         self.out_dir = out_dir
         os.makedirs(out_dir, exist_ok=True)
@@ -65,7 +70,8 @@ def main(argv=None) -> int:
     parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
     parser.add_argument("--max-tokens", type=int, required=True,
-                        help="most tokens live requests hold at any time, each rounded up to 64")
+                        help="most tokens live requests hold at any time (the pool also has room for 64 partly "
+                             "filled pages)")
     parser.add_argument("--device", default="cuda:0")
     args = parser.parse_args(argv)
 
