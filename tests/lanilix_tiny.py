@@ -53,6 +53,15 @@ CONFIGS = {
         {"type": "delta", "mixer": delta(2, 1, 40, 8, 1), "mlp": mlp(32, 1.0)},
         {"type": "attention", "mixer": attention(8, 1, 32, 0.25, rot=(2, 100.0), mask=(5, 0)), "mlp": mlp(96, 2.5)},
     ]),
+    # nothing a multiple of eight: width 100, key size 20 with six taps, five heads; a head size of
+    # 48 with three heads on one kv head and full rotation; a head size of 40 (no tensor-core
+    # kernel takes it) with more kept positions than the window holds
+    "s": dict(vocab=333, width=100, eps=2e-5, stored="bfloat16", seed=14, layers=[
+        {"type": "delta", "mixer": delta(5, 5, 20, 12, 6), "mlp": mlp(70, 1.2)},
+        {"type": "attention", "mixer": attention(3, 1, 48, 0.2, rot=(48, 20000.0), mask=(130, 1)), "mlp": mlp(70, 5.0)},
+        {"type": "attention", "mixer": attention(2, 2, 40, 0.22, rot=(6, 300.0), mask=(7, 9)), "mlp": None},
+        {"type": "delta", "mixer": delta(5, 5, 20, 12, 6), "mlp": mlp(70, 1.2), "weights_of": 0},
+    ]),
 }
 
 

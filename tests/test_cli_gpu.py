@@ -54,3 +54,23 @@ def test_generate_and_bench_from_a_named_configuration():
                                                   "--repeats", "1")]
     assert [line["shape"] for line in lines] == ["2x16x8", "1x40x5"]
     assert all(line["tok_per_s"] > 0 and line["ttft_ms"] > 0 for line in lines)
+
+
+def test_the_other_architecture_from_the_command_line(tmp_path):
+    """The same sub-commands on a Lanilix configuration: a folder written by ``random-model``
+    is read back by ``generate``, chosen by the ``architecture`` key of its config.json, and
+    prints the entry point's tokens."""
+    from thing_htn_2026_b200 import Engine, cli
+    folder = str(tmp_path / "lanilix")
+    assert run_cli("random-model", "--random-config", "lanilix-tiny", "--seed", "2", "--out", folder, "--dtype",
+                   "bfloat16") == [folder]
+    with open(os.path.join(folder, "config.json")) as handle:
+        assert json.load(handle)["architecture"] == "Lanilix"
+    printed = [json.loads(line) for line in run_cli("generate", "--model", folder, "--prompt-lens", "3,70,21", "--seed", "5",
+                                                    "--max-new-tokens", "9", "--dtype", "float32")]
+    engine = Engine(folder, dtype="float32")
+    steps = list(engine.generate(cli.make_prompts_of([3, 70, 21], engine.model.vocab_size, 5), 9))
+    assert [p["tokens"] for p in printed] == [[step[j] for step in steps] for j in range(3)]
+    lines = [json.loads(line) for line in run_cli("bench", "--random-config", "lanilix-tiny", "--layers", "2", "--shapes",
+                                                  "2x16x8", "--repeats", "1")]
+    assert lines[0]["shape"] == "2x16x8" and lines[0]["tok_per_s"] > 0

@@ -206,7 +206,8 @@ class Stepper:
         return [y[a:b] for a, b in zip(cu[:-1], cu[1:])]
 
 
-MIXERS = [("p", 0), ("p", 1), ("q", 0), ("q", 1), ("q", 2), ("q", 3), ("r", 0), ("r", 1), ("r", 2)]
+MIXERS = [("p", 0), ("p", 1), ("q", 0), ("q", 1), ("q", 2), ("q", 3), ("r", 0), ("r", 1), ("r", 2), ("s", 0), ("s", 1),
+          ("s", 2)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
