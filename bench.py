@@ -628,7 +628,7 @@ def kernel_table(torch, lan, peak, batch, context):
     slots = cache.open(batch + 1)
     conv_w, a_log, dt_bias = rnd(shape.conv_channels, shape.taps) * 0.5, rnd(Hd) - 3.0, rnd(Hd)
     state, ring = cache.state_view(0, 0), cache.state_view(0, 1)
-    for n, who, tag in ((T, [slots[0]], "prefill"), (1, slots[1:], "decode")):
+    for n, who, tag in ((T, [slots[0]], "prefill"), (1, slots[1:], "decode"), (T, slots[1:], f"prefill of {batch} prompts")):
         cu = torch.arange(len(who) + 1, dtype=torch.int32, device=dev) * n
         slots_dev = torch.tensor(who, dtype=torch.int32, device=dev)
         rows_ = ops.step_rows(cu, slots_dev, cache.seq_lens, n * len(who), n)
@@ -638,7 +638,9 @@ def kernel_table(torch, lan, peak, batch, context):
         row(f"{tag}: delta_rule (conv, norms, recurrence)",
             lambda: ops.delta_rule(proj, conv_w, a_log, dt_bias, state, ring, rows_, cache.seq_lens, shape, 1e-6),
             nbytes=state_bytes + tokens * (shape.proj_width * 2 + Hd * dv * 4), flops=6.0 * tokens * Hd * dk * dv,
-            flop_peak=FP32_CORE_TFLOPS * 1e12, like=f"{tag}: attention (all keys)")
+            flop_peak=FP32_CORE_TFLOPS * 1e12, like=f"{tag}: attention (all keys)" if len(tag) < 8 else None)
+        if len(tag) >= 8:
+            continue
         o = rnd(tokens, Hd, dv)
         wn = 1 + rnd(dv) * 0.1
         row(f"{tag}: gated_head_norm", lambda: ops.gated_head_norm(o, proj, shape.gate_offset, wn, 1e-6, Hd, dv, bf),

@@ -148,6 +148,74 @@ def test_gated_head_norm(dtype):
     close(got, want.reshape(rows, -1), dtype, "gated head norm")
 
 
+def rotate_reference(x, positions, dims, base, layout):
+    """x [T, heads, d]; the first ``dims`` entries of each head rotated by position * base^(-2i/dims),
+    entry i paired with entry i + dims / 2 ("half") or entry 2i with 2i + 1 ("interleaved")."""
+    if layout == "interleaved":
+        return plain.rotate_pairs(x, positions, dims, base)
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    angle = positions.to(torch.float32)[:, None] * (base ** (-2.0 * i / dims)).to(torch.float32)[None, :]
+    c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+    lo, hi = x[..., :dims // 2], x[..., dims // 2:dims]
+    out = x.clone()
+    out[..., :dims // 2] = lo * c - hi * s
+    out[..., dims // 2:dims] = hi * c + lo * s
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("scope", [None, "head", "projection"])
+@pytest.mark.parametrize("layout", ["half", "interleaved"])
+@pytest.mark.parametrize("n_q, n_kv, d, dims, own_values", [(4, 2, 64, 32, False), (3, 1, 48, 48, True), (2, 2, 40, 12, False),
+                                                           (5, 5, 9, 4, True), (2, 1, 128, 6, False)])
+def test_query_and_key_preparation_alone(dtype, scope, layout, n_q, n_kv, d, dims, own_values):
+    """`ops.qk_prepare`: norm per head, over the whole projection or none; rotation of the first
+    `dims` entries with either pairing; the values from the row or from the keys as projected;
+    head sizes that are even (two entries per thread) and odd (one), rotations whose half is odd."""
+    from thing_htn_2026_b200 import ops
+    from thing_htn_2026_b200.cache import KVSpec, SequenceCache
+    t = TORCH[dtype]
+    T, eps, base = 70, 1e-5, 777.0
+    width = (n_q + (2 if own_values else 1) * n_kv) * d + (0 if (n_q + n_kv) % 2 else 2)    # also rows longer than needed
+    proj = rand((T, width), 31 + d).to(t)
+    gq = 1 + rand((n_q * d if scope == "projection" else d,), 32, 0.2)
+    gk = 1 + rand((n_kv * d if scope == "projection" else d,), 33, 0.2)
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    inv_freq = (base ** (-2.0 * i / dims)).to(torch.float32).to(DEV)
+    cos, sin = torch.empty((128, dims // 2), device=DEV), torch.empty((128, dims // 2), device=DEV)
+    ops.rope_table(cos, sin, inv_freq, 0, 128)
+    tables = ops.RotaryTables(cos, sin, dims, layout)
+    cache = SequenceCache([KVSpec(n_kv, d)], max_tokens=128, dtype=t, device=DEV, max_slots=2)
+    (slot,) = cache.open(1)
+    cache.prepare([slot], [T])
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    rows = ops.step_rows(cu, torch.tensor([slot], dtype=torch.int32, device=DEV), cache.seq_lens, T, T)
+    err = ops.new_error_word(DEV)
+    q = ops.qk_prepare(proj.to(DEV), gq.to(DEV) if scope else None, gk.to(DEV) if scope else None, scope, eps, tables,
+                       rows, cache.kv_view(0), n_q, not own_values, True, err)
+    assert int(err.item()) == 0
+    x = proj.float()
+    q_raw, k_raw = x[:, :n_q * d], x[:, n_q * d:(n_q + n_kv) * d]
+    v_raw = x[:, (n_q + n_kv) * d:(n_q + 2 * n_kv) * d] if own_values else k_raw
+    if scope == "projection":
+        q_n, k_n = plain.norm_plain_weight(q_raw, gq, eps), plain.norm_plain_weight(k_raw, gk, eps)
+    elif scope == "head":
+        q_n = plain.norm_plain_weight(q_raw.reshape(T, n_q, d), gq, eps).reshape(T, -1)
+        k_n = plain.norm_plain_weight(k_raw.reshape(T, n_kv, d), gk, eps).reshape(T, -1)
+    else:
+        q_n, k_n = q_raw, k_raw
+    positions = torch.arange(T)
+    want_q = rotate_reference(q_n.reshape(T, n_q, d), positions, dims, base, layout).reshape(T, -1)
+    want_k = rotate_reference(k_n.reshape(T, n_kv, d), positions, dims, base, layout)
+    close(q, want_q, dtype, "queries")
+    pages = cache.book.pages_of(0, slot)
+    storage = cache.kv_view(0).storage.float().cpu()                  # [pages, 2, n_kv, 64, d]
+    got_k = torch.cat([storage[pages[p], 0] for p in sorted(pages)], dim=1)[:, :T].transpose(0, 1)
+    got_v = torch.cat([storage[pages[p], 1] for p in sorted(pages)], dim=1)[:, :T].transpose(0, 1)
+    close(got_k, want_k, dtype, "keys in the cache")
+    assert torch.equal(got_v, v_raw.to(t).float().reshape(T, n_kv, d)), "values are copied untouched"
+
+
 def part_of(folder, layer_index, member, dtype):
     """One member part of a layer of a written model, built as the model builds it, with the
     checkpoint's tensors and the layer's own config entry."""

@@ -14,10 +14,154 @@
 #include "common.cuh"
 
 namespace {
-constexpr int kMaxThreads = 512;
 
+// Two sums over a block at once; every thread gets both.  The order of additions depends on
+// the block size only.
+template <int THREADS>
+__device__ __forceinline__ float2 block_sum2(float a, float b, float* scratch /* >= 66 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (lane == 0) { scratch[warp] = a; scratch[32 + warp] = b; }
+    __syncthreads();
+    if (warp == 0) {
+        float ta = lane < THREADS / 32 ? scratch[lane] : 0.f, tb = lane < THREADS / 32 ? scratch[32 + lane] : 0.f;
+        ta = warp_sum(ta);
+        tb = warp_sum(tb);
+        if (lane == 0) { scratch[64] = ta; scratch[65] = tb; }
+    }
+    __syncthreads();
+    return make_float2(scratch[64], scratch[65]);
+}
+
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+    static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+    static __device__ __forceinline__ void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+template <> struct Pair<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+        return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+    }
+};
+
+// One block of THREADS per row.  A thread takes pairs of adjacent entries (2j, 2j + 1): head
+// sizes are even here (the launcher sends odd ones to the scalar kernel below), so a pair never
+// straddles two heads, an interleaved rotation has both partners in one thread, and every
+// access is 4 or 8 bytes wide.  Pass 1 stages the row in shared memory and sums the squares
+// (and copies the values to the cache); pass 2 normalises, rotates and stores.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS) qk_prepare_kernel(
+    T* __restrict__ q_out, const T* __restrict__ proj, int proj_width, const float* __restrict__ q_gain,
+    const float* __restrict__ k_gain, int norm_scope, float gain_offset, float eps, const float* __restrict__ cos_tab,
+    const float* __restrict__ sin_tab, int table_len, int rotary_dim, int interleaved, int values_are_keys,
+    const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_q, int write_cache,
+    int half_d_shift, int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(8) float vals[];   // [(n_q + n_kv) * D] raw values; then [n_q + n_kv] scales per head
+    __shared__ float scratch[66];
+    const int m = blockIdx.x;
+    const int D = kv.head_dim, half_d = D >> 1;
+    const int nq = n_q * D, nk = kv.n_kv * D, total = nq + nk, n_heads = n_q + kv.n_kv;
+    float* head_scale = vals + total;
+    const T* src = proj + (size_t)m * proj_width;
+    const int pos = row_pos[m];
+    int page = -1;
+    if (write_cache) {
+        page = kv.block_table[(size_t)row_slot[m] * kv.bt_stride + pos / kv.page_size];
+        if (page < 0) {
+            if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
+            write_cache = 0;
+        }
+    }
+    const int in_page = pos % kv.page_size;
+    auto head_of = [&](int pair) { return half_d_shift >= 0 ? pair >> half_d_shift : pair / half_d; };
+
+    float ss_q = 0.f, ss_k = 0.f;
+    for (int pair = threadIdx.x; pair < total / 2; pair += THREADS) {
+        const int e = 2 * pair;
+        const float2 v = Pair<T>::load(src + e);
+        *reinterpret_cast<float2*>(vals + e) = v;
+        const float sq = v.x * v.x + v.y * v.y;
+        if (e < nq) ss_q += sq; else ss_k += sq;
+        if (write_cache && (values_are_keys ? e >= nq : false)) {     // the keys as projected are the values
+            const int kvh = head_of(pair) - n_q, d = e - nq - kvh * D;
+            Pair<T>::store((T*)kv.base + kv_offset(kv, page, 1, kvh, in_page) + d, v.x, v.y);
+        }
+    }
+    if (write_cache && !values_are_keys) {
+        for (int pair = threadIdx.x; pair < nk / 2; pair += THREADS) {
+            const int e = 2 * pair, kvh = e / D, d = e - kvh * D;
+            const float2 v = Pair<T>::load(src + total + e);
+            Pair<T>::store((T*)kv.base + kv_offset(kv, page, 1, kvh, in_page) + d, v.x, v.y);
+        }
+    }
+    float rq = 1.f, rk = 1.f;
+    if (norm_scope == 2) {
+        const float2 t = block_sum2<THREADS>(ss_q, ss_k, scratch);
+        rq = 1.0f / sqrtf(t.x / (float)nq + eps);
+        rk = 1.0f / sqrtf(t.y / (float)nk + eps);
+    } else {
+        __syncthreads();
+        if (norm_scope == 1) {
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+            for (int head = warp; head < n_heads; head += THREADS / 32) {
+                float ss = 0.f;
+                for (int d = lane; d < D; d += 32) ss += vals[head * D + d] * vals[head * D + d];
+                ss = warp_sum(ss);
+                if (lane == 0) head_scale[head] = 1.0f / sqrtf(ss / (float)D + eps);
+            }
+            __syncthreads();
+        }
+    }
+    const bool rotate = cos_tab != nullptr && rotary_dim > 0;
+    if (rotate && pos >= table_len) {
+        if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_POSITION_RANGE);
+        return;
+    }
+    const int half = rotary_dim / 2;
+    // the normalised value of entry e of the row (head, entry d of it)
+    auto normed = [&](int e, int head, int d) {
+        const bool is_q = e < nq;
+        float v = vals[e];
+        if (norm_scope == 2) v *= (is_q ? rq : rk) * (gain_offset + (is_q ? q_gain[e] : k_gain[e - nq]));
+        else if (norm_scope == 1) v *= head_scale[head] * (gain_offset + (is_q ? q_gain[d] : k_gain[d]));
+        return v;
+    };
+    for (int pair = threadIdx.x; pair < total / 2; pair += THREADS) {
+        const int e = 2 * pair, head = head_of(pair), d = e - head * D;
+        if (e >= nq && !write_cache) continue;
+        float a = normed(e, head, d), b = normed(e + 1, head, d + 1);
+        if (rotate && d < rotary_dim) {
+            const float* c_row = cos_tab + (size_t)pos * half;
+            const float* s_row = sin_tab + (size_t)pos * half;
+            if (interleaved) {
+                const float c = c_row[d >> 1], s = s_row[d >> 1];
+                const float ra = a * c - b * s, rb = b * c + a * s;
+                a = ra; b = rb;
+            } else {
+                // entries d and d + 1 are both in the first half or both in the second (half is whole
+                // pairs only when rotary_dim / 2 is even; else the scalar kernel runs)
+                const bool first = d < half;
+                const int i = first ? d : d - half, other = first ? e + half : e - half;
+                const float pa = normed(other, head, first ? d + half : d - half);
+                const float pb = normed(other + 1, head, (first ? d + half : d - half) + 1);
+                a = first ? a * c_row[i] - pa * s_row[i] : a * c_row[i] + pa * s_row[i];
+                b = first ? b * c_row[i + 1] - pb * s_row[i + 1] : b * c_row[i + 1] + pb * s_row[i + 1];
+            }
+        }
+        if (e < nq) Pair<T>::store(q_out + (size_t)m * nq + e, a, b);
+        else Pair<T>::store((T*)kv.base + kv_offset(kv, page, 0, head - n_q, in_page) + d, a, b);
+    }
+}
+
+// Any sizes (odd head sizes, odd row widths, a rotation whose half is odd): one entry at a time.
 template <typename T>
-__global__ void __launch_bounds__(kMaxThreads) qk_prepare_kernel(
+__global__ void __launch_bounds__(128) qk_prepare_scalar_kernel(
     T* __restrict__ q_out, const T* __restrict__ proj, int proj_width, const float* __restrict__ q_gain,
     const float* __restrict__ k_gain, int norm_scope, float gain_offset, float eps, const float* __restrict__ cos_tab,
     const float* __restrict__ sin_tab, int table_len, int rotary_dim, int interleaved, int values_are_keys,
@@ -25,7 +169,7 @@ __global__ void __launch_bounds__(kMaxThreads) qk_prepare_kernel(
     int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float vals[];          // [(n_q + n_kv) * D]: q heads, then k heads
+    extern __shared__ __align__(8) float vals[];
     __shared__ float scratch[33];
     const int m = blockIdx.x;
     const int D = kv.head_dim;
@@ -48,7 +192,6 @@ __global__ void __launch_bounds__(kMaxThreads) qk_prepare_kernel(
         }
     }
     const int in_page = pos % kv.page_size;
-    // values: untouched copies
     if (write_cache) {
         for (int e = threadIdx.x; e < nk; e += blockDim.x) {
             const int kvh = e / D, d = e - kvh * D;
@@ -88,7 +231,7 @@ __global__ void __launch_bounds__(kMaxThreads) qk_prepare_kernel(
             int i, partner;
             bool first;
             if (interleaved) {
-                i = d >> 1; first = (d & 1) == 0; partner = e ^ 1;
+                i = d >> 1; first = (d & 1) == 0; partner = first ? e + 1 : e - 1;
             } else {
                 first = d < half; i = first ? d : d - half; partner = first ? e + half : e - half;
             }
@@ -109,23 +252,36 @@ int launch(void* q_out, const void* proj, int proj_width, const float* q_gain, c
            float gain_offset, float eps, const float* cos_tab, const float* sin_tab, int table_len, int rotary_dim,
            int interleaved, int values_are_keys, const int* row_slot, const int* row_pos, PagedKV kv, int n_rows,
            int n_q, int write_cache, int* err, cudaStream_t stream) {
-    const size_t smem = (size_t)(n_q + kv.n_kv) * kv.head_dim * sizeof(float);
-    if (smem > 48 * 1024) {
-        THN_UNSUPPORTED_IF(smem > 200 * 1024, "qk_prepare: %d heads of %d do not fit shared memory", n_q + kv.n_kv,
-                           kv.head_dim);
-        cudaFuncSetAttribute(qk_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int D = kv.head_dim, n_heads = n_q + kv.n_kv;
+    const size_t smem = ((size_t)n_heads * D + n_heads) * sizeof(float);
+    THN_UNSUPPORTED_IF(smem > 200 * 1024, "qk_prepare: %d heads of %d do not fit shared memory", n_heads, D);
+    // pairs of adjacent entries need even sizes everywhere and pair-aligned addresses
+    const bool pairs = D % 2 == 0 && proj_width % 2 == 0 && (interleaved || (rotary_dim / 2) % 2 == 0) &&
+                       (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)kv.base) & (2 * sizeof(T) - 1)) == 0;
+    if (!pairs) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(qk_prepare_scalar_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        thn_launch(qk_prepare_scalar_kernel<T>, n_rows, 128, smem, stream, (T*)q_out, (const T*)proj, proj_width, q_gain,
+                   k_gain, norm_scope, gain_offset, eps, cos_tab, sin_tab, table_len, rotary_dim, interleaved,
+                   values_are_keys, row_slot, row_pos, kv, n_q, write_cache, err);
+        return thn_launch_status("qk_prepare");
     }
-    const int total = (n_q + kv.n_kv) * kv.head_dim;
-    // few rows (single-token steps): the row's latency counts, four values per thread; many rows:
-    // 128 threads, more blocks per SM (28.6 against 43.0 us for 2,048 rows of 20 heads of 128)
-    int threads = 128;
-    if (n_rows <= 64) {
-        threads = ((total + 3) / 4 + 31) / 32 * 32;
-        threads = threads < 128 ? 128 : threads > kMaxThreads ? kMaxThreads : threads;
-    }
-    thn_launch(qk_prepare_kernel<T>, n_rows, threads, smem, stream, (T*)q_out, (const T*)proj, proj_width, q_gain,
-               k_gain, norm_scope, gain_offset, eps, cos_tab, sin_tab, table_len, rotary_dim, interleaved,
-               values_are_keys, row_slot, row_pos, kv, n_q, write_cache, err);
+    int shift = -1;
+    if (((D / 2) & (D / 2 - 1)) == 0) for (shift = 0; (1 << shift) < D / 2; ++shift) {}
+    // few rows (single-token steps): the row's latency counts, 512 threads; many rows: 128 threads
+    // and more blocks per SM, 256 for rows of 4,096 entries or more
+#define THN_QK_LAUNCH(THREADS)                                                                                        \
+    do {                                                                                                              \
+        if (smem > 48 * 1024)                                                                                         \
+            cudaFuncSetAttribute(qk_prepare_kernel<T, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        thn_launch(qk_prepare_kernel<T, THREADS>, n_rows, THREADS, smem, stream, (T*)q_out, (const T*)proj, proj_width, \
+                   q_gain, k_gain, norm_scope, gain_offset, eps, cos_tab, sin_tab, table_len, rotary_dim, interleaved, \
+                   values_are_keys, row_slot, row_pos, kv, n_q, write_cache, shift, err);                             \
+    } while (0)
+    if (n_rows <= 64 && n_heads * D >= 2048) THN_QK_LAUNCH(512);
+    else if (n_heads * D >= 4096) THN_QK_LAUNCH(256);
+    else THN_QK_LAUNCH(128);
+#undef THN_QK_LAUNCH
     return thn_launch_status("qk_prepare");
 }
 }  // namespace
