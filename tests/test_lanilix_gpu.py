@@ -135,15 +135,17 @@ def test_norms_around_a_float32_stream(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_gated_head_norm(dtype):
+@pytest.mark.parametrize("heads, size, offset, tail", [(3, 40, 11, 3), (3, 40, 12, 0), (2, 128, 64, 4), (1, 320, 0, 0), (4, 9, 5, 1)])
+def test_gated_head_norm(dtype, heads, size, offset, tail):
+    """Sizes and gate offsets that take the 16-byte kernel and ones that do not."""
     from thing_htn_2026_b200 import ops
     t = TORCH[dtype]
-    rows, heads, size = 7, 3, 40
+    rows = 7
     o = rand((rows, heads, size), 5, 4.0)
-    gate = rand((rows, 11 + heads * size + 3), 6).to(t)
+    gate = rand((rows, offset + heads * size + tail), 6).to(t)
     w = 1 + rand((size,), 7, 0.2)
-    got = ops.gated_head_norm(o.to(DEV), gate.to(DEV), 11, w.to(DEV), 1e-5, heads, size, t)
-    z = gate[:, 11:11 + heads * size].float().reshape(rows, heads, size)
+    got = ops.gated_head_norm(o.to(DEV), gate.to(DEV), offset, w.to(DEV), 1e-5, heads, size, t)
+    z = gate[:, offset:offset + heads * size].float().reshape(rows, heads, size)
     want = plain.norm_plain_weight(o, w, 1e-5) * plain.silu(z)
     close(got, want.reshape(rows, -1), dtype, "gated head norm")
 
