@@ -62,6 +62,11 @@ CONFIGS = {
         {"type": "attention", "mixer": attention(2, 2, 40, 0.22, rot=(6, 300.0), mask=(7, 9)), "mlp": None},
         {"type": "delta", "mixer": delta(5, 5, 20, 12, 6), "mlp": mlp(70, 1.2), "weights_of": 0},
     ]),
+    # a key size above 256 (64 registers of state per lane), with and without 16-byte accesses
+    "t": dict(vocab=64, width=32, eps=1e-5, stored="float32", seed=15, layers=[
+        {"type": "delta", "mixer": delta(2, 1, 264, 8, 2), "mlp": None},
+        {"type": "delta", "mixer": delta(1, 1, 259, 20, 3), "mlp": mlp(48, 2.0)},
+    ]),
 }
 
 

@@ -277,7 +277,7 @@ class Stepper:
 
 
 MIXERS = [("p", 0), ("p", 1), ("q", 0), ("q", 1), ("q", 2), ("q", 3), ("r", 0), ("r", 1), ("r", 2), ("s", 0), ("s", 1),
-          ("s", 2)]
+          ("s", 2), ("t", 0), ("t", 1)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

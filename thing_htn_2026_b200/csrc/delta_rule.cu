@@ -5,13 +5,14 @@
 //     S <- g S;   u = b (v - S^T k);   S <- S + k u^T;   o = S^T q
 //
 // so the read-out sees the token's own write.  Every column of S (one entry of v, u and o)
-// evolves on its own, which is what the kernels use: a column is held by 8 lanes of a warp,
-// dk / 8 values each, in registers, for all the tokens a step brings.
+// evolves on its own, which is what the kernels use: a column is held by 8 (or 32) lanes of a
+// warp, a few values of the key axis each, in registers, for all the tokens a step brings.
 //
-// Three kernels: `prepare` (the short causal convolutions of q, k and v over time with their
-// silu, the unit norms, b and g: one block per row), `recurrence` (one block per sequence,
-// head and 16 columns; it also moves the convolution's window of raw inputs on) and, for
-// steps of one token per sequence, `decode`, which does both in one launch.  The state, the
+// Steps of several tokens per sequence run three kernels: `prepare` (the short causal
+// convolutions of q, k and v over time with their silu, the unit norms, b and g: one block per
+// row), `recurrence` (one block per sequence, head and group of columns) and `ring update`
+// (the convolution's window of raw inputs moves on, once nothing reads it any more).  Steps of
+// one token per sequence run `decode`, which does all of it in one launch.  The state, the
 // unit norms, b, g and all sums are float32; the projections come in the activation type.
 //
 // Per-sequence state.  S: float32 [slots, heads, dv, dk] (a column's dk values contiguous).
@@ -446,7 +447,7 @@ int check_shape(const DeltaShape& s, const char* what) {
     THN_CHECK_ARG(s.n_heads > 0 && s.n_kv > 0 && s.dk > 0 && s.dv > 0 && s.taps > 0, "%s: bad sizes", what);
     THN_CHECK_ARG(s.n_heads % s.n_kv == 0, "%s: %d heads are not a multiple of %d key heads", what, s.n_heads, s.n_kv);
     THN_CHECK_ARG(s.proj_width >= s.a_offset() + s.n_heads, "%s: projected rows of %d are too short", what, s.proj_width);
-    THN_UNSUPPORTED_IF(s.dk > 256, "%s: key size %d above 256", what, s.dk);
+    THN_UNSUPPORTED_IF(s.dk > 512, "%s: key size %d above 512", what, s.dk);
     return THN_OK;
 }
 
@@ -488,7 +489,8 @@ void launch_decode(float* o, float* state, void* ring, const void* proj, const f
         if (s.dk <= 32) { if (vec) CALL(4, 4); else CALL(4, 1); }          \
         else if (s.dk <= 64) { if (vec) CALL(8, 4); else CALL(8, 1); }     \
         else if (s.dk <= 128) { if (vec) CALL(16, 4); else CALL(16, 1); }  \
-        else { if (vec) CALL(32, 4); else CALL(32, 1); }                   \
+        else if (s.dk <= 256) { if (vec) CALL(32, 4); else CALL(32, 1); }  \
+        else { if (vec) CALL(64, 4); else CALL(64, 1); }                   \
     } while (0)
 
 }  // namespace
@@ -549,8 +551,10 @@ THN_API int thn_delta_recurrence(float* o, float* state, const float* qn, const 
         CALL32(2, 1);
     } else if (dk <= 128) {
         if (vec) CALL32(4, 4); else CALL32(4, 1);
-    } else {
+    } else if (dk <= 256) {
         if (vec) CALL32(8, 4); else CALL32(8, 1);
+    } else {
+        THN_DELTA_DISPATCH(CALL8);        // key sizes above 256: 8 lanes of 64 registers
     }
 #undef CALL8
 #undef CALL32
