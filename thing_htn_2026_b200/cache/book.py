@@ -2,9 +2,11 @@
 
 The cache is made of *groups*.  A group is a set of cache entries (one per layer that
 writes a cache) with the same needs; it has storage and a page allocator of its own.
-Two kinds of need exist for keys and values: all positions, or a window of the last W
-positions.  A windowed group gives pages back as soon as every position in them has
-fallen out of the window, so a long sequence holds about W / page_size pages there.  A
+Three kinds of need exist for keys and values: all positions, a window of the last W
+positions, or chunks of C positions of which a query reads only its own.  A windowed group
+gives pages back as soon as every position in them has fallen out of the window, so a long
+sequence holds about W / page_size pages there; a chunked group gives back the pages that lie
+wholly before the chunk of the next position.  A
 windowed group may also keep the first ``keep_first`` positions of every sequence for good:
 the pages that hold them are never given back while the sequence lives.
 
@@ -33,6 +35,7 @@ class GroupBook:
     window: Optional[int]   # None: all positions are kept
     n_pages: int
     keep_first: int = 0     # with a window: positions [0, keep_first) stay readable for good
+    chunk: Optional[int] = None   # a query reads its own chunk of this many positions only
 
 
 class CacheBook:
@@ -86,10 +89,13 @@ class CacheBook:
 
     def _first_needed_page(self, g: int, next_position: int) -> int:
         """Lowest logical page that a query at ``next_position`` or later can still read."""
-        window = self.groups[g].window
-        if window is None:
-            return 0
-        return max(0, next_position - window + 1) // self.page_size
+        window, chunk = self.groups[g].window, self.groups[g].chunk
+        first = 0
+        if window is not None:
+            first = max(0, next_position - window + 1)
+        if chunk:
+            first = max(first, next_position // chunk * chunk)
+        return first // self.page_size
 
     def pages_needed(self, slot: int, n_new: int) -> List[int]:
         """How many new pages each group needs to take ``n_new`` more tokens."""

@@ -3,7 +3,8 @@ of fixed size, and the device copies of block tables and lengths.
 
 Storage of a key/value group: ``[entries, pages, 2, n_kv, page_size, head_dim]`` (K then
 V inside a page, head-major, so the ``page_size * head_dim`` values of one head of one
-page are contiguous).  The reference's layout is ``[B, Nkv, CAP, D]`` per layer
+page are contiguous).  Where values have a size of their own a page is flat: the K block
+``[n_kv, page_size, head_dim]``, then the V block ``[n_kv, page_size, value_dim]``.  The reference's layout is ``[B, Nkv, CAP, D]`` per layer
 (engine/engine.py:844-846); pages replace the fixed capacity so that sequences of very
 different lengths share one pool.
 
@@ -31,12 +32,21 @@ PAGE_SIZE = 64
 @dataclass(frozen=True)
 class KVSpec:
     """A mixer's need for keys and values: ``window=None`` keeps all positions; with a window,
-    the first ``keep_first`` positions of a sequence stay readable as well."""
+    the first ``keep_first`` positions of a sequence stay readable as well.  ``chunk``: a query
+    reads only the positions of its own chunk of that many positions (chunks counted from the
+    sequence's start), so whole chunks behind the current one are given back.  ``value_dim``:
+    the size of a value where it differs from a key's (None: ``head_dim``)."""
 
     n_kv: int
     head_dim: int
     window: Optional[int] = None
     keep_first: int = 0
+    chunk: Optional[int] = None
+    value_dim: Optional[int] = None
+
+    def __post_init__(self):
+        if self.value_dim == self.head_dim:
+            object.__setattr__(self, "value_dim", None)
 
 
 @dataclass(frozen=True)
@@ -91,13 +101,14 @@ class SequenceCache:
                 counts[key] = counts.get(key, 0) + 1
             self._entry_place[entry] = places
 
-        self.book = CacheBook([GroupBook(spec.window, n_pages, spec.keep_first if spec.window else 0)
+        self.book = CacheBook([GroupBook(spec.window, n_pages, spec.keep_first if spec.window else 0, spec.chunk)
                                for spec in self.kv_specs], page_size, self.max_slots, self.max_pages_per_seq)
         # Zeroed once: pages are never cleared afterwards, but what lies beyond a sequence's
         # length must stay finite (a masked key's weight is 0, and 0 * NaN would poison V).
         self.kv_storage = [
-            torch.zeros((counts[("kv", g)], n_pages, 2, spec.n_kv, page_size, spec.head_dim), dtype=dtype,
-                        device=self.device)
+            torch.zeros((counts[("kv", g)], n_pages, 2, spec.n_kv, page_size, spec.head_dim) if spec.value_dim is None
+                        else (counts[("kv", g)], n_pages, spec.n_kv * page_size * (spec.head_dim + spec.value_dim)),
+                        dtype=dtype, device=self.device)
             for g, spec in enumerate(self.kv_specs)
         ]
         self.block_tables = [torch.full((self.max_slots, self.max_pages_per_seq), -1, dtype=torch.int32,
@@ -123,7 +134,8 @@ class SequenceCache:
         if kind != "kv":
             raise KeyError(f"cache entry {entry} holds state, not keys and values")
         spec = self.kv_specs[g]
-        return ops.KVView(self.kv_storage[g][i], self.block_tables[g], spec.n_kv, self.page_size, spec.head_dim)
+        return ops.KVView(self.kv_storage[g][i], self.block_tables[g], spec.n_kv, self.page_size, spec.head_dim,
+                          spec.value_dim)
 
     def state_view(self, entry: int, part: int = 0) -> torch.Tensor:
         """The entry's state tensor ``[max_slots, *shape]`` (the ``part``-th, where its need is a

@@ -10,25 +10,29 @@
 // multiplies V; the float32 sum of e divides at the end; query head h reads kv head
 // h / (n_q / n_kv).  Row at position p sees keys j <= p, and j > p - window when a
 // window is set (the reference has no window); with a window, the first keep_first keys of
-// the sequence stay visible to every later row, at their own positions.
+// the sequence stay visible to every later row, at their own positions.  With a chunk size C
+// instead, a row sees the keys j <= p of its own chunk only: floor(j / C) = floor(p / C),
+// chunks counted from position 0 of the sequence.  Values may have a size of their own
+// (kv.value_dim); the output then has that size per head.  exact_weights keeps e in float32
+// where it multiplies V.
 #include <math.h>
 
 #include "common.cuh"
 
-constexpr int kGenericMaxPerLane = 16;  // head_dim <= 512
+constexpr int kGenericMaxPerLane = 16;  // head_dim, value_dim <= 512
 
 template <typename T, int PER_LANE>
 __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q,
                                          const int* __restrict__ row_slot, const int* __restrict__ row_pos,
                                          PagedKV kv, int n_rows, int n_q, float scale, int window,
-                                         int keep_first, int* __restrict__ err) {
+                                         int keep_first, int chunk, int exact_weights, int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= (long long)n_rows * n_q) return;
     const int m = (int)(unit / n_q), h = (int)(unit - (long long)m * n_q);
-    const int D = kv.head_dim;
+    const int D = kv.head_dim, DV = kv.value_dim > 0 ? kv.value_dim : kv.head_dim;
     const int kvh = h / (n_q / kv.n_kv);
     const int pos = row_pos[m];
     const int* pages = kv.block_table + (size_t)row_slot[m] * kv.bt_stride;
@@ -43,6 +47,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
     float run_max = -INFINITY, run_sum = 0.f;
     int first = 0;
     if (window > 0 && pos - window + 1 > 0) first = pos - window + 1;
+    if (chunk > 0) first = max(first, pos / chunk * chunk);
 
     int page_index = -1;
     const T* k_page = nullptr;
@@ -57,10 +62,10 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
                 if (lane == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
                 return;
             }
-            k_page = (const T*)kv.base + kv_offset(kv, page, 0, kvh, 0);
-            v_page = (const T*)kv.base + kv_offset(kv, page, 1, kvh, 0);
+            k_page = (const T*)kv.base + kv_offset_sized(kv, page, 0, kvh, 0);
+            v_page = (const T*)kv.base + kv_offset_sized(kv, page, 1, kvh, 0);
         }
-        const size_t in_page = (size_t)(j % kv.page_size) * D;
+        const size_t in_page = (size_t)(j % kv.page_size) * D, in_page_v = (size_t)(j % kv.page_size) * DV;
         float dot = 0.f;
 #pragma unroll
         for (int i = 0; i < PER_LANE; ++i) {
@@ -72,31 +77,32 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
         const float correction = expf(run_max - new_max);  // 0 on the first key
         const float e = expf(s - new_max);
         run_sum = run_sum * correction + e;
-        const float p = rnd<T>(e);
+        const float p = exact_weights ? e : rnd<T>(e);
 #pragma unroll
         for (int i = 0; i < PER_LANE; ++i) {
             const int d = lane + 32 * i;
-            if (d < D) acc[i] = acc[i] * correction + p * to_f32<T>(v_page[in_page + d]);
+            if (d < DV) acc[i] = acc[i] * correction + p * to_f32<T>(v_page[in_page_v + d]);
         }
         run_max = new_max;
     }
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) {
         const int d = lane + 32 * i;
-        if (d < D) out[(size_t)m * n_q * D + (size_t)h * D + d] = from_f32<T>(acc[i] / run_sum);
+        if (d < DV) out[(size_t)m * n_q * DV + (size_t)h * DV + d] = from_f32<T>(acc[i] / run_sum);
     }
 }
 
 template <typename T>
 static int launch_generic(void* out, const void* q, const int* row_slot, const int* row_pos, PagedKV kv, int n_rows,
-                          int n_q, float scale, int window, int keep_first, int* err, cudaStream_t stream) {
+                          int n_q, float scale, int window, int keep_first, int chunk, int exact_weights, int* err,
+                          cudaStream_t stream) {
     const int warps = 4;
     const long long units = (long long)n_rows * n_q;
     const unsigned blocks = (unsigned)((units + warps - 1) / warps);
-    const int per_lane = (kv.head_dim + 31) / 32;
+    const int per_lane = (max(kv.head_dim, kv.value_dim) + 31) / 32;
 #define LAUNCH(N)                                                                                                  \
     thn_launch(attention_generic_kernel<T, N>, blocks, warps * 32, 0, stream, (T*)out, (const T*)q, row_slot, row_pos, kv, \
-                                                                      n_rows, n_q, scale, window, keep_first, err)
+                                                                      n_rows, n_q, scale, window, keep_first, chunk, exact_weights, err)
     if (per_lane <= 1) LAUNCH(1);
     else if (per_lane <= 2) LAUNCH(2);
     else if (per_lane <= 4) LAUNCH(4);
@@ -106,22 +112,27 @@ static int launch_generic(void* out, const void* q, const int* row_slot, const i
     return thn_launch_status("attention_generic");
 }
 
-// q, out [n_rows, n_q * head_dim]; the keys of a row are positions [.., row_pos] of the
-// sequence in row_slot, already in the cache.  window <= 0 means all keys (keep_first is
-// then without effect).
+// q [n_rows, n_q * head_dim], out [n_rows, n_q * value_dim]; the keys of a row are positions
+// [.., row_pos] of the sequence in row_slot, already in the cache.  window <= 0 means all keys
+// (keep_first is then without effect); chunk > 0: only the keys of the row's own chunk;
+// value_dim 0: values of the keys' size.
 THN_API int thn_attention_generic(void* out, const void* q, const int* row_slot, const int* row_pos,
                                   const void* kv_base, const int* block_table, int bt_stride, int n_kv,
-                                  int page_size, int head_dim, int n_rows, int n_q, float scale, int window,
-                                  int keep_first, int dtype, int* err, cudaStream_t stream) {
+                                  int page_size, int head_dim, int value_dim, int n_rows, int n_q, float scale,
+                                  int window, int keep_first, int chunk, int exact_weights, int dtype, int* err,
+                                  cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && n_q > 0 && n_kv > 0 && page_size > 0, "attention_generic: bad sizes");
     THN_CHECK_ARG(n_q % n_kv == 0, "attention_generic: %d query heads are not a multiple of %d kv heads", n_q, n_kv);
-    THN_UNSUPPORTED_IF(head_dim <= 0 || head_dim > 32 * kGenericMaxPerLane,
-                       "attention_generic: head_dim %d not in [1, %d]", head_dim, 32 * kGenericMaxPerLane);
+    THN_UNSUPPORTED_IF(head_dim <= 0 || head_dim > 32 * kGenericMaxPerLane || value_dim < 0 ||
+                           value_dim > 32 * kGenericMaxPerLane,
+                       "attention_generic: head_dim %d or value_dim %d not in [1, %d]", head_dim, value_dim,
+                       32 * kGenericMaxPerLane);
+    THN_CHECK_ARG(chunk <= 0 || keep_first <= 0, "attention_generic: kept first keys go with a window, not with chunks");
     if (n_rows == 0) return THN_OK;
-    PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim};
-    if (dtype == THN_F32) return launch_generic<float>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, err, stream);
+    PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim, value_dim == head_dim ? 0 : value_dim};
+    if (dtype == THN_F32) return launch_generic<float>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, chunk, exact_weights, err, stream);
     if (dtype == THN_BF16)
-        return launch_generic<__nv_bfloat16>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, err, stream);
+        return launch_generic<__nv_bfloat16>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, chunk, exact_weights, err, stream);
     THN_CHECK_ARG(false, "attention_generic: unknown dtype %d", dtype);
     return THN_OK;
 }

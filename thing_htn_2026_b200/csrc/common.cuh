@@ -162,7 +162,8 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 }
 
 // Geometry of one cache entry: pages of page_size tokens; inside a page K then V, each
-// [n_kv][page_size][head_dim].
+// [n_kv][page_size][head_dim] (V: [n_kv][page_size][value_dim] where values have a size of
+// their own; kernels that take such entries address them with kv_offset_sized).
 struct PagedKV {
     const void* base;      // first byte of this entry's pool
     const int* block_table;  // [max_slots][bt_stride] physical page of (slot, logical page), -1 = unmapped
@@ -170,8 +171,19 @@ struct PagedKV {
     int n_kv;
     int page_size;
     int head_dim;
+    int value_dim;         // size of a value where it differs from a key's; 0: the same (head_dim)
 };
 
 __device__ __forceinline__ long long kv_offset(const PagedKV& kv, int page, int which, int kvh, int in_page) {
     return ((((long long)page * 2 + which) * kv.n_kv + kvh) * kv.page_size + in_page) * (long long)kv.head_dim;
+}
+
+// The same for entries whose values may have a size of their own: element offset of key
+// (which = 0) or value (which = 1) `in_page` of kv head `kvh` in `page`.
+__device__ __forceinline__ long long kv_offset_sized(const PagedKV& kv, int page, int which, int kvh, int in_page) {
+    const long long dv = kv.value_dim > 0 ? kv.value_dim : kv.head_dim;
+    const long long k_block = (long long)kv.n_kv * kv.page_size * kv.head_dim;
+    const long long page_base = (long long)page * (k_block + (long long)kv.n_kv * kv.page_size * dv);
+    if (which == 0) return page_base + ((long long)kvh * kv.page_size + in_page) * kv.head_dim;
+    return page_base + k_block + ((long long)kvh * kv.page_size + in_page) * dv;
 }

@@ -60,6 +60,72 @@ THN_API int thn_gather_rows(void* out, const void* table, const int* index, int 
     return thn_launch_status("gather_rows");
 }
 
+// out[m] = float(table[index[m]]) * scale in float32: token embeddings that start a residual
+// stream kept in float32.
+template <typename T>
+__global__ void gather_rows_scaled_kernel(float* __restrict__ out, const T* __restrict__ table,
+                                          const int* __restrict__ index, int width, int n_table_rows, float scale,
+                                          int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int m = blockIdx.x;
+    int row = index[m];
+    if (row < 0 || row >= n_table_rows) {
+        if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_TOKEN_RANGE);
+        row = 0;
+    }
+    const T* src = table + (size_t)row * width;
+    float* dst = out + (size_t)m * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_f32<T>(src[i]) * scale;
+}
+
+THN_API int thn_gather_rows_scaled(float* out, const void* table, const int* index, int n_rows, int width,
+                                   int n_table_rows, float scale, int dtype, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_rows >= 0 && width > 0 && n_table_rows > 0, "gather_rows_scaled: bad sizes rows=%d width=%d table=%d",
+                  n_rows, width, n_table_rows);
+    if (n_rows == 0) return THN_OK;
+    if (dtype == THN_F32)
+        thn_launch(gather_rows_scaled_kernel<float>, n_rows, 256, 0, stream, out, (const float*)table, index, width,
+                   n_table_rows, scale, err);
+    else if (dtype == THN_BF16)
+        thn_launch(gather_rows_scaled_kernel<__nv_bfloat16>, n_rows, 256, 0, stream, out, (const __nv_bfloat16*)table, index,
+                   width, n_table_rows, scale, err);
+    else
+        THN_CHECK_ARG(false, "gather_rows_scaled: unknown dtype %d", dtype);
+    return thn_launch_status("gather_rows_scaled");
+}
+
+// out[m, i] = a[m, i] * logistic(g[m, i]): an output gate on a mixer's concatenated heads.  The
+// gate's rows are g_stride elements apart (it may be a slice of a wider projected row).
+template <typename T>
+__global__ void logistic_gate_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ g,
+                                     long long g_stride, long long n, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const long long m = e / width;
+    const float z = to_f32<T>(g[m * g_stride + (e - m * width)]);
+    out[e] = from_f32<T>(to_f32<T>(a[e]) / (1.0f + expf(-z)));
+}
+
+THN_API int thn_logistic_gate(void* out, const void* a, const void* g, long long g_stride, int n_rows, int width,
+                              int dtype, cudaStream_t stream) {
+    THN_CHECK_ARG(n_rows >= 0 && width > 0 && g_stride >= width, "logistic_gate: bad sizes");
+    const long long n = (long long)n_rows * width;
+    if (n == 0) return THN_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == THN_F32)
+        thn_launch(logistic_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)a, (const float*)g,
+                   g_stride, n, width);
+    else if (dtype == THN_BF16)
+        thn_launch(logistic_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a,
+                   (const __nv_bfloat16*)g, g_stride, n, width);
+    else
+        THN_CHECK_ARG(false, "logistic_gate: unknown dtype %d", dtype);
+    return thn_launch_status("logistic_gate");
+}
+
 // ------------------------------------------------------------------ RMSNorm
 
 constexpr int kNormThreads = 256;

@@ -1,0 +1,166 @@
+// Routing of a mixture of experts, and the experts' activation with the routing weights.
+//
+//   moe_route   per row: scores s = softmax(z) over all experts; the experts form `groups` equal
+//               groups of neighbours, a group's score is its largest s, and only experts of the
+//               `keep` best groups can be chosen; the `top` allowed experts with the largest s
+//               are chosen (the lower index wins a tie); a chosen expert's weight is s * scale,
+//               not renormalised.  Writes the weights as a dense row [experts] (0 where not
+//               chosen) and as lists chosen [top], chosen_weight [top].  float32 throughout.
+//   routed_gelu the up-projections of all experts side by side, [experts * ff | shared_ff] per
+//               row: out = gelu(u) * weight of the column's expert, and for the shared expert's
+//               columns gelu(u) * logistic(gate logit of the row).  gelu is the exact one,
+//               0.5 u (1 + erf(u / sqrt 2)).  An expert that was not chosen gets zeros, so one
+//               down-projection over all columns gives the weighted sum of the chosen experts'
+//               outputs plus the gated shared expert's.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kRouteWarps = 4;
+
+struct Best {
+    float value;
+    int index;
+};
+
+__device__ __forceinline__ Best warp_best(Best b) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v = __shfl_xor_sync(0xffffffffu, b.value, o);
+        const int i = __shfl_xor_sync(0xffffffffu, b.index, o);
+        if (v > b.value || (v == b.value && i < b.index)) { b.value = v; b.index = i; }
+    }
+    return b;
+}
+
+__global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
+    float* __restrict__ dense, int* __restrict__ chosen, float* __restrict__ chosen_weight, const float* __restrict__ z,
+    long long z_stride, int n_rows, int n_experts, int n_groups, int keep, int top, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float shared[];     // per warp: scores [experts], group scores [groups]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * kRouteWarps + warp;
+    if (row >= n_rows) return;
+    float* s = shared + (size_t)warp * (n_experts + n_groups);
+    float* group_score = s + n_experts;
+    const float* zr = z + (size_t)row * z_stride;
+    const int per = n_experts / n_groups;
+
+    float mx = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, zr[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < n_experts; e += 32) {
+        const float v = expf(zr[e] - mx);
+        s[e] = v;
+        sum += v;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < n_experts; e += 32) {
+        s[e] = s[e] / sum;
+        dense[(size_t)row * n_experts + e] = 0.f;
+    }
+    __syncwarp();
+    for (int g = lane; g < n_groups; g += 32) {
+        float best = -1.f;
+        for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, s[e]);
+        group_score[g] = best;
+    }
+    __syncwarp();
+    // the `keep` best groups stay as they are; the scores of the others are hidden behind a sign
+    if (keep < n_groups) {
+        for (int round = 0; round < keep; ++round) {
+            Best b{-1.f, 0x7fffffff};
+            for (int g = lane; g < n_groups; g += 32)
+                if (group_score[g] > b.value) { b.value = group_score[g]; b.index = g; }
+            b = warp_best(b);
+            __syncwarp();
+            if (lane == 0) group_score[b.index] = -2.f;      // taken
+            __syncwarp();
+        }
+        for (int e = lane; e < n_experts; e += 32)
+            if (group_score[e / per] != -2.f) s[e] = -1.f - s[e];      // not allowed; the score is kept, negative
+        __syncwarp();
+    }
+    for (int round = 0; round < top; ++round) {
+        Best b{-1.f, 0x7fffffff};
+        for (int e = lane; e < n_experts; e += 32)
+            if (s[e] > b.value) { b.value = s[e]; b.index = e; }
+        b = warp_best(b);
+        __syncwarp();
+        if (lane == 0) {
+            const float w = b.value * scale;
+            dense[(size_t)row * n_experts + b.index] = w;
+            chosen[(size_t)row * top + round] = b.index;
+            chosen_weight[(size_t)row * top + round] = w;
+            s[b.index] = -4.f;       // taken
+        }
+        __syncwarp();
+    }
+}
+
+__device__ __forceinline__ float gelu_exact(float u) { return 0.5f * u * (1.0f + erff(u * 0.70710678118654752f)); }
+
+template <typename T>
+__global__ void routed_gelu_kernel(T* __restrict__ out, const T* __restrict__ u, const float* __restrict__ dense,
+                                   const float* __restrict__ shared_logit, long long logit_stride, long long n, int width,
+                                   int n_experts, int ff) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const long long row = e / width;
+    const int c = (int)(e - row * width);
+    float w;
+    if (c < n_experts * ff) {
+        w = dense[row * n_experts + c / ff];
+        if (w == 0.f) { out[e] = from_f32<T>(0.f); return; }
+    } else {
+        w = shared_logit ? 1.0f / (1.0f + expf(-shared_logit[row * logit_stride])) : 1.0f;
+    }
+    out[e] = from_f32<T>(gelu_exact(to_f32<T>(u[e])) * w);
+}
+
+}  // namespace
+
+// z float32 [rows, >= experts] with rows z_stride apart; dense float32 [rows, experts]; chosen
+// int32 and chosen_weight float32 [rows, top].
+THN_API int thn_moe_route(float* dense, int* chosen, float* chosen_weight, const float* z, long long z_stride, int n_rows,
+                          int n_experts, int n_groups, int keep, int top, float scale, cudaStream_t stream) {
+    THN_CHECK_ARG(n_rows >= 0 && n_experts > 0 && n_groups > 0 && n_experts % n_groups == 0,
+                  "moe_route: %d experts in %d groups", n_experts, n_groups);
+    THN_CHECK_ARG(keep > 0 && keep <= n_groups && top > 0 && top <= keep * (n_experts / n_groups),
+                  "moe_route: top %d of the experts of %d groups out of %d", top, keep, n_groups);
+    THN_UNSUPPORTED_IF(n_experts > 4096, "moe_route: %d experts, at most 4096", n_experts);
+    if (n_rows == 0) return THN_OK;
+    const size_t smem = (size_t)kRouteWarps * (n_experts + n_groups) * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    thn_launch(moe_route_kernel, (n_rows + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, stream, dense, chosen,
+               chosen_weight, z, z_stride, n_rows, n_experts, n_groups, keep, top, scale);
+    return thn_launch_status("moe_route");
+}
+
+// u, out [rows, experts * ff + shared_ff] of the activation type; dense float32 [rows, experts];
+// shared_logit: the rows' gate logits of the shared expert, logit_stride apart (null: no gate).
+THN_API int thn_routed_gelu(void* out, const void* u, const float* dense, const float* shared_logit, long long logit_stride,
+                            int n_rows, int n_experts, int ff, int shared_ff, int dtype, cudaStream_t stream) {
+    THN_CHECK_ARG(n_rows >= 0 && n_experts >= 0 && ff >= 0 && shared_ff >= 0 && n_experts * ff + shared_ff > 0,
+                  "routed_gelu: bad sizes");
+    const int width = n_experts * ff + shared_ff;
+    const long long n = (long long)n_rows * width;
+    if (n == 0) return THN_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == THN_F32)
+        thn_launch(routed_gelu_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)u, dense, shared_logit,
+                   logit_stride, n, width, n_experts, ff);
+    else if (dtype == THN_BF16)
+        thn_launch(routed_gelu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)u,
+                   dense, shared_logit, logit_stride, n, width, n_experts, ff);
+    else
+        THN_CHECK_ARG(false, "routed_gelu: unknown dtype %d", dtype);
+    return thn_launch_status("routed_gelu");
+}

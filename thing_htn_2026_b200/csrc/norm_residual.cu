@@ -1,23 +1,52 @@
 // Norms around a residual stream that is kept in float32 whatever the activation type is,
-// with an optional norm of the branch output before it is added ("sandwich" arrangement):
+// with an optional norm of the branch output before it is added:
 //
-//     h <- h + B(d),   B(d) = d                                        (no post gain)
-//                      B(d) = d / sqrt(mean(d^2) + eps_b) * (o_b + w_b)  (post gain w_b)
-//     y  = h / sqrt(mean(h^2) + eps) * (o + w)                          (gain w; else no y)
+//     h <- h + B(d),   B(d) = d                                                  (post kind 0)
+//                      B(d) = d / sqrt(mean(d^2) + eps_b) * (o_b + w_b)          (post kind 1, RMS)
+//                      B(d) = (d - mean d) / sqrt(var d + eps_b) * (o_b + w_b) + b_b   (post kind 2, layer norm)
+//     y  = N(h) with N of kind 1 or 2 as above (gain w, bias b), or
+//     y  = h rounded to the activation type (kind 3: the stream itself is what a sublayer reads), or
+//     no y (kind 0).
 //
 // o_b and o are gain offsets: 0 for a gain stored as it multiplies, 1 for a gain stored around
-// zero.  Every sum, both square roots and the residual sum are float32; y is rounded once to
-// the activation type T.  One block per row, the row staged in shared memory; the order of
-// additions depends on the block size only, so a row's result does not depend on its batch.
+// zero; a bias may be absent.  The variance is the mean of the squared deviations from the mean
+// (two passes over the staged row).  Every sum, both square roots and the residual sum are
+// float32; y is rounded once to the activation type T.  One block per row, the row staged in
+// shared memory; the order of additions depends on the block size only, so a row's result does
+// not depend on its batch.
 #include "common.cuh"
 
 namespace {
 constexpr int kThreads = 256;
 
+struct NormArgs {
+    const float* gain;
+    const float* bias;
+    float offset;
+    float eps;
+    int kind;     // 0 none, 1 RMS, 2 layer norm, 3 (output only) the stream as it is
+};
+
+// (mean, 1 / sqrt(var + eps)) of the staged row for a norm of the given kind; mean is 0 for RMS.
+__device__ __forceinline__ float2 row_statistics(const float* row, int width, int kind, float eps, float* scratch) {
+    float mean = 0.f;
+    if (kind == 2) {
+        float s = 0.f;
+        for (int i = threadIdx.x; i < width; i += kThreads) s += row[i];
+        mean = block_sum(s, scratch) / (float)width;
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += kThreads) {
+        const float c = row[i] - mean;
+        ss += c * c;
+    }
+    const float total = block_sum(ss, scratch);
+    return make_float2(mean, 1.0f / sqrtf(total / (float)width + eps));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads) residual_norm_kernel(
-    T* __restrict__ y, float* __restrict__ h, const T* __restrict__ d, const float* __restrict__ post_gain,
-    float post_offset, float post_eps, const float* __restrict__ gain, float offset, float eps, int width,
+    T* __restrict__ y, float* __restrict__ h, const T* __restrict__ d, NormArgs post, NormArgs out, int width,
     int h_is_new) {
     pdl_launch_dependents();
     pdl_wait();
@@ -25,20 +54,18 @@ __global__ void __launch_bounds__(kThreads) residual_norm_kernel(
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * width;
     if (d) {
-        float ss = 0.f;
-        for (int i = threadIdx.x; i < width; i += kThreads) {
-            const float v = to_f32<T>(d[base + i]);
-            row[i] = v;
-            ss += v * v;
-        }
-        float r = 1.f;
-        if (post_gain) {
-            const float total = block_sum(ss, scratch);
-            r = 1.0f / sqrtf(total / (float)width + post_eps);
+        for (int i = threadIdx.x; i < width; i += kThreads) row[i] = to_f32<T>(d[base + i]);
+        float2 st = make_float2(0.f, 1.f);
+        if (post.kind) {
+            __syncthreads();
+            st = row_statistics(row, width, post.kind, post.eps, scratch);
         }
         for (int i = threadIdx.x; i < width; i += kThreads) {
             float v = row[i];
-            if (post_gain) v = v * r * (post_offset + post_gain[i]);
+            if (post.kind) {
+                v = (v - st.x) * st.y * (post.offset + post.gain[i]);
+                if (post.bias) v += post.bias[i];
+            }
             if (!h_is_new) v = h[base + i] + v;
             h[base + i] = v;
             row[i] = v;
@@ -46,36 +73,41 @@ __global__ void __launch_bounds__(kThreads) residual_norm_kernel(
     } else {
         for (int i = threadIdx.x; i < width; i += kThreads) row[i] = h[base + i];
     }
-    if (!gain) return;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += kThreads) ss += row[i] * row[i];
-    const float total = block_sum(ss, scratch);
-    const float rstd = 1.0f / sqrtf(total / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += kThreads)
-        y[base + i] = from_f32<T>(row[i] * rstd * (offset + gain[i]));
+    if (!out.kind) return;
+    if (out.kind == 3) {
+        for (int i = threadIdx.x; i < width; i += kThreads) y[base + i] = from_f32<T>(row[i]);
+        return;
+    }
+    __syncthreads();
+    const float2 st = row_statistics(row, width, out.kind, out.eps, scratch);
+    for (int i = threadIdx.x; i < width; i += kThreads) {
+        float v = (row[i] - st.x) * st.y * (out.offset + out.gain[i]);
+        if (out.bias) v += out.bias[i];
+        y[base + i] = from_f32<T>(v);
+    }
 }
 
 template <typename T>
-int launch(void* y, float* h, const void* d, const float* post_gain, float post_offset, float post_eps,
-           const float* gain, float offset, float eps, int rows, int width, int h_is_new, cudaStream_t stream) {
+int launch(void* y, float* h, const void* d, NormArgs post, NormArgs out, int rows, int width, int h_is_new,
+           cudaStream_t stream) {
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 48 * 1024) {
         THN_UNSUPPORTED_IF(smem > 200 * 1024, "residual_norm: rows of %d values do not fit shared memory", width);
         cudaFuncSetAttribute(residual_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
-    thn_launch(residual_norm_kernel<T>, rows, kThreads, smem, stream, (T*)y, h, (const T*)d, post_gain, post_offset,
-               post_eps, gain, offset, eps, width, h_is_new);
+    thn_launch(residual_norm_kernel<T>, rows, kThreads, smem, stream, (T*)y, h, (const T*)d, post, out, width, h_is_new);
     return thn_launch_status("residual_norm");
 }
 
-// out[m, :] = d[m, :] / sqrt(mean(d[m, :]^2) + eps) * w * silu(gate[m, :]) per group of `size`
+// out[m, :] = d[m, :] / sqrt(mean(d[m, :]^2) + eps) * w * act(gate[m, :]) per group of `size`
 // values: the read-out of a head of a recurrent mixer, normalised over the head, with one gain
-// vector shared by the heads and a gate taken from `gate` (row stride gate_stride).  One warp
-// per (row, head); float32 inside, rounded once.
+// vector shared by the heads (w_stride 0) or one per head (w_stride = size) and a gate taken
+// from `gate` (row stride gate_stride); act is silu (gate_kind 0) or the logistic function
+// (gate_kind 1).  One warp per (row, head); float32 inside, rounded once.
 template <typename T>
 __global__ void gated_head_norm_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate,
                                        long long gate_stride, const float* __restrict__ w, float eps, long long n_units,
-                                       int n_heads, int size) {
+                                       int n_heads, int size, int w_stride, int gate_kind) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -89,9 +121,11 @@ __global__ void gated_head_norm_kernel(T* __restrict__ out, const float* __restr
     ss = warp_sum(ss);
     const float rstd = 1.0f / sqrtf(ss / (float)size + eps);
     const T* g = gate + m * gate_stride + (long long)head * size;
+    const float* wh = w + (size_t)head * w_stride;
     for (int i = lane; i < size; i += 32) {
         const float z = to_f32<T>(g[i]);
-        out[unit * size + i] = from_f32<T>(src[i] * rstd * w[i] * (z / (1.0f + expf(-z))));
+        const float logistic = 1.0f / (1.0f + expf(-z));
+        out[unit * size + i] = from_f32<T>(src[i] * rstd * wh[i] * (gate_kind ? logistic : z * logistic));
     }
 }
 // The same with four consecutive entries per lane (16-byte loads of the read-out, 8-byte loads
@@ -135,36 +169,42 @@ __global__ void gated_head_norm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out,
 }  // namespace
 
 // h float32 [rows, width], updated in place when d is given (h_is_new: h is not read, it
-// becomes B(d)); d and y of the activation type; gains float32 [width].  post_gain may be
-// null (d is added as it is); gain may be null (no y is written).
-THN_API int thn_residual_norm(void* y, float* h, const void* d, const float* post_gain, float post_offset,
-                              float post_eps, const float* gain, float offset, float eps, int rows, int width,
-                              int h_is_new, int dtype, cudaStream_t stream) {
+// becomes B(d)); d and y of the activation type; gains and biases float32 [width] (a bias may
+// be null).  post_kind 0: d is added as it is; kind 0: no y is written; kind 3: y is h rounded.
+THN_API int thn_residual_norm(void* y, float* h, const void* d, const float* post_gain, const float* post_bias,
+                              float post_offset, float post_eps, int post_kind, const float* gain, const float* bias,
+                              float offset, float eps, int kind, int rows, int width, int h_is_new, int dtype,
+                              cudaStream_t stream) {
     THN_CHECK_ARG(rows >= 0 && width > 0, "residual_norm: bad sizes rows=%d width=%d", rows, width);
-    THN_CHECK_ARG(h != nullptr && (d != nullptr || gain != nullptr), "residual_norm: nothing to do");
+    THN_CHECK_ARG(post_kind >= 0 && post_kind <= 2 && kind >= 0 && kind <= 3, "residual_norm: norm kinds %d, %d", post_kind,
+                  kind);
+    THN_CHECK_ARG(h != nullptr && (d != nullptr || kind != 0), "residual_norm: nothing to do");
     THN_CHECK_ARG(d != nullptr || !h_is_new, "residual_norm: a new residual stream needs a branch to start from");
-    THN_CHECK_ARG(gain == nullptr || (y != nullptr && eps > 0.f), "residual_norm: gain without y, or eps <= 0");
-    THN_CHECK_ARG(post_gain == nullptr || post_eps > 0.f, "residual_norm: post eps must be positive");
+    THN_CHECK_ARG(kind == 0 || y != nullptr, "residual_norm: an output norm without y");
+    THN_CHECK_ARG(!(kind == 1 || kind == 2) || (gain != nullptr && eps > 0.f), "residual_norm: gain missing, or eps <= 0");
+    THN_CHECK_ARG(post_kind == 0 || (post_gain != nullptr && post_eps > 0.f), "residual_norm: post gain missing, or eps <= 0");
     if (rows == 0) return THN_OK;
-    if (dtype == THN_F32)
-        return launch<float>(y, h, d, post_gain, post_offset, post_eps, gain, offset, eps, rows, width, h_is_new, stream);
-    if (dtype == THN_BF16)
-        return launch<__nv_bfloat16>(y, h, d, post_gain, post_offset, post_eps, gain, offset, eps, rows, width,
-                                     h_is_new, stream);
+    const NormArgs post{post_gain, post_bias, post_offset, post_eps, d ? post_kind : 0};
+    const NormArgs out{gain, bias, offset, eps, kind};
+    if (dtype == THN_F32) return launch<float>(y, h, d, post, out, rows, width, h_is_new, stream);
+    if (dtype == THN_BF16) return launch<__nv_bfloat16>(y, h, d, post, out, rows, width, h_is_new, stream);
     THN_CHECK_ARG(false, "residual_norm: unknown dtype %d", dtype);
     return THN_OK;
 }
 
 // o float32 [rows, n_heads, size]; gate of the activation type, row stride gate_stride
-// elements; w float32 [size]; out of the activation type [rows, n_heads * size].
+// elements; w float32 [size] (w_per_head 0) or [n_heads * size] (w_per_head 1); gate_kind 0: silu,
+// 1: logistic; out of the activation type [rows, n_heads * size].
 THN_API int thn_gated_head_norm(void* out, const float* o, const void* gate, long long gate_stride, const float* w,
-                                float eps, int rows, int n_heads, int size, int dtype, cudaStream_t stream) {
+                                float eps, int rows, int n_heads, int size, int w_per_head, int gate_kind, int dtype,
+                                cudaStream_t stream) {
     THN_CHECK_ARG(rows >= 0 && n_heads > 0 && size > 0 && eps > 0.f, "gated_head_norm: bad sizes");
     const long long units = (long long)rows * n_heads;
     if (units == 0) return THN_OK;
     const int warps = 4;
     const unsigned blocks = (unsigned)((units + warps - 1) / warps);
-    if (dtype == THN_BF16 && size % 4 == 0 && gate_stride % 4 == 0 &&
+    const int w_stride = w_per_head ? size : 0;
+    if (dtype == THN_BF16 && !w_per_head && gate_kind == 0 && size % 4 == 0 && gate_stride % 4 == 0 &&
         ((((uintptr_t)o | (uintptr_t)w) & 15) | (((uintptr_t)gate | (uintptr_t)out) & 7)) == 0) {
         thn_launch(gated_head_norm_bf16_vec_kernel, blocks, warps * 32, 0, stream, (__nv_bfloat16*)out, o,
                    (const __nv_bfloat16*)gate, gate_stride, w, eps, units, n_heads, size);
@@ -172,10 +212,10 @@ THN_API int thn_gated_head_norm(void* out, const float* o, const void* gate, lon
     }
     if (dtype == THN_F32)
         thn_launch(gated_head_norm_kernel<float>, blocks, warps * 32, 0, stream, (float*)out, o, (const float*)gate,
-                   gate_stride, w, eps, units, n_heads, size);
+                   gate_stride, w, eps, units, n_heads, size, w_stride, gate_kind);
     else if (dtype == THN_BF16)
         thn_launch(gated_head_norm_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)out, o,
-                   (const __nv_bfloat16*)gate, gate_stride, w, eps, units, n_heads, size);
+                   (const __nv_bfloat16*)gate, gate_stride, w, eps, units, n_heads, size, w_stride, gate_kind);
     else
         THN_CHECK_ARG(false, "gated_head_norm: unknown dtype %d", dtype);
     return thn_launch_status("gated_head_norm");

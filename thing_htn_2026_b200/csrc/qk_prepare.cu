@@ -9,7 +9,8 @@
 //                0: entry i is paired with entry i + rotary_dim / 2 (rotate-half);
 //                1: entry 2i is paired with entry 2i + 1 (interleaved).
 //                The pair (a, b) with angle t becomes (a cos t - b sin t, b cos t + a sin t).
-//   values       0: the row brings values of its own, [q | k | v];
+//   values       0: the row brings values of its own, [q | k | v] (a value may have a size of its
+//                   own, value_dim);
 //                1: the values are the keys as projected, before norm and rotation, [q | k].
 #include "common.cuh"
 
@@ -90,14 +91,15 @@ __global__ void __launch_bounds__(THREADS) qk_prepare_kernel(
         if (e < nq) ss_q += sq; else ss_k += sq;
         if (write_cache && (values_are_keys ? e >= nq : false)) {     // the keys as projected are the values
             const int kvh = head_of(pair) - n_q, d = e - nq - kvh * D;
-            Pair<T>::store((T*)kv.base + kv_offset(kv, page, 1, kvh, in_page) + d, v.x, v.y);
+            Pair<T>::store((T*)kv.base + kv_offset_sized(kv, page, 1, kvh, in_page) + d, v.x, v.y);
         }
     }
     if (write_cache && !values_are_keys) {
-        for (int pair = threadIdx.x; pair < nk / 2; pair += THREADS) {
-            const int e = 2 * pair, kvh = e / D, d = e - kvh * D;
+        const int DV = kv.value_dim > 0 ? kv.value_dim : D;
+        for (int pair = threadIdx.x; pair < kv.n_kv * DV / 2; pair += THREADS) {
+            const int e = 2 * pair, kvh = e / DV, d = e - kvh * DV;
             const float2 v = Pair<T>::load(src + total + e);
-            Pair<T>::store((T*)kv.base + kv_offset(kv, page, 1, kvh, in_page) + d, v.x, v.y);
+            Pair<T>::store((T*)kv.base + kv_offset_sized(kv, page, 1, kvh, in_page) + d, v.x, v.y);
         }
     }
     float rq = 1.f, rk = 1.f;
@@ -155,7 +157,7 @@ __global__ void __launch_bounds__(THREADS) qk_prepare_kernel(
             }
         }
         if (e < nq) Pair<T>::store(q_out + (size_t)m * nq + e, a, b);
-        else Pair<T>::store((T*)kv.base + kv_offset(kv, page, 0, head - n_q, in_page) + d, a, b);
+        else Pair<T>::store((T*)kv.base + kv_offset_sized(kv, page, 0, head - n_q, in_page) + d, a, b);
     }
 }
 
@@ -193,10 +195,11 @@ __global__ void __launch_bounds__(128) qk_prepare_scalar_kernel(
     }
     const int in_page = pos % kv.page_size;
     if (write_cache) {
-        for (int e = threadIdx.x; e < nk; e += blockDim.x) {
-            const int kvh = e / D, d = e - kvh * D;
+        const int DV = !values_are_keys && kv.value_dim > 0 ? kv.value_dim : D;
+        for (int e = threadIdx.x; e < kv.n_kv * DV; e += blockDim.x) {
+            const int kvh = e / DV, d = e - kvh * DV;
             const T v = values_are_keys ? src[nq + e] : src[total + e];
-            ((T*)kv.base)[kv_offset(kv, page, 1, kvh, in_page) + d] = v;
+            ((T*)kv.base)[kv_offset_sized(kv, page, 1, kvh, in_page) + d] = v;
         }
     }
     if (norm_scope == 2) {
@@ -242,7 +245,7 @@ __global__ void __launch_bounds__(128) qk_prepare_scalar_kernel(
             q_out[(size_t)m * nq + e] = from_f32<T>(out);
         } else if (write_cache) {
             const int kvh = head - n_q;
-            ((T*)kv.base)[kv_offset(kv, page, 0, kvh, in_page) + d] = from_f32<T>(out);
+            ((T*)kv.base)[kv_offset_sized(kv, page, 0, kvh, in_page) + d] = from_f32<T>(out);
         }
     }
 }
@@ -256,7 +259,7 @@ int launch(void* q_out, const void* proj, int proj_width, const float* q_gain, c
     const size_t smem = ((size_t)n_heads * D + n_heads) * sizeof(float);
     THN_UNSUPPORTED_IF(smem > 200 * 1024, "qk_prepare: %d heads of %d do not fit shared memory", n_heads, D);
     // pairs of adjacent entries need even sizes everywhere and pair-aligned addresses
-    const bool pairs = D % 2 == 0 && proj_width % 2 == 0 && (interleaved || (rotary_dim / 2) % 2 == 0) &&
+    const bool pairs = D % 2 == 0 && kv.value_dim % 2 == 0 && proj_width % 2 == 0 && (interleaved || (rotary_dim / 2) % 2 == 0) &&
                        (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)kv.base) & (2 * sizeof(T) - 1)) == 0;
     if (!pairs) {
         if (smem > 48 * 1024)
@@ -290,17 +293,19 @@ THN_API int thn_qk_prepare(void* q_out, const void* proj, int proj_width, const 
                            int norm_scope, float gain_offset, float eps, const float* cos_tab, const float* sin_tab,
                            int table_len, int rotary_dim, int interleaved, int values_are_keys, const int* row_slot,
                            const int* row_pos, void* kv_base, const int* block_table, int bt_stride, int n_kv,
-                           int page_size, int head_dim, int n_rows, int n_q, int write_cache, int dtype, int* err,
-                           cudaStream_t stream) {
+                           int page_size, int head_dim, int value_dim, int n_rows, int n_q, int write_cache, int dtype,
+                           int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && n_q > 0 && n_kv > 0 && head_dim > 0 && page_size > 0, "qk_prepare: bad sizes");
     THN_CHECK_ARG(norm_scope >= 0 && norm_scope <= 2, "qk_prepare: norm scope %d", norm_scope);
     THN_CHECK_ARG(norm_scope == 0 || (q_gain && k_gain && eps > 0.f), "qk_prepare: a norm needs gains and eps");
     THN_CHECK_ARG(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
                   "qk_prepare: rotary_dim %d must be even and within the head size %d", rotary_dim, head_dim);
-    THN_CHECK_ARG(proj_width >= (n_q + (values_are_keys ? 1 : 2) * n_kv) * head_dim, "qk_prepare: rows of %d are too short",
-                  proj_width);
+    if (value_dim <= 0) value_dim = head_dim;
+    THN_CHECK_ARG(!values_are_keys || value_dim == head_dim, "qk_prepare: values that are the keys have the keys' size");
+    THN_CHECK_ARG(proj_width >= (n_q + n_kv) * head_dim + (values_are_keys ? 0 : n_kv * value_dim),
+                  "qk_prepare: rows of %d are too short", proj_width);
     if (n_rows == 0) return THN_OK;
-    PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim};
+    PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim, value_dim == head_dim ? 0 : value_dim};
     if (dtype == THN_F32)
         return launch<float>(q_out, proj, proj_width, q_gain, k_gain, norm_scope, gain_offset, eps, cos_tab, sin_tab,
                              table_len, rotary_dim, interleaved, values_are_keys, row_slot, row_pos, kv, n_rows, n_q,

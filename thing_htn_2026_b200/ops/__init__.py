@@ -55,15 +55,28 @@ _SIGNATURES = {
                                         c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_int,
                                         c_void_p, c_void_p],
     "thn_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                              c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
-    "thn_residual_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_float, c_float, c_int,
-                          c_int, c_int, c_int, c_void_p],
+                              c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "thn_residual_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p, c_void_p,
+                          c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "thn_gated_head_norm": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_int, c_int, c_int, c_int,
-                            c_void_p],
+                            c_int, c_int, c_void_p],
+    "thn_gather_rows_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "thn_logistic_gate": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
+    "thn_latent_norm": [c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_int, c_int, c_int, c_void_p],
+    "thn_latent_assemble": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p, c_void_p],
+    "thn_mlstm_columns_per_block": [],
+    "thn_mlstm_gates": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
+    "thn_mlstm_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
+    "thn_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
+                      c_void_p],
+    "thn_routed_gelu": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "thn_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p],
     "thn_qk_prepare": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                       c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                       c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "thn_delta_prepare": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_float, c_int, c_void_p],
@@ -274,6 +287,31 @@ def gather_rows(table: torch.Tensor, index: torch.Tensor, err: Optional[torch.Te
     return out
 
 
+def gather_rows_scaled(table: torch.Tensor, index: torch.Tensor, scale: float,
+                       err: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[m] = float32(table[index[m]]) * scale: rows that start a residual stream kept in float32."""
+    _need(table, "gather_rows_scaled table")
+    _need(index, "gather_rows_scaled index", torch.int32)
+    out = torch.empty((index.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+    _call("thn_gather_rows_scaled", _ptr(out), _ptr(table), _ptr(index), index.shape[0], table.shape[1], table.shape[0],
+          float(scale), _code(table, "gather_rows_scaled"), _ptr(err), _stream())
+    return out
+
+
+def logistic_gate(a: torch.Tensor, gate: torch.Tensor, gate_offset: int = 0) -> torch.Tensor:
+    """a [rows, width] * logistic(gate[:, gate_offset : gate_offset + width]); the gate may be a
+    slice of a wider projected row."""
+    _need(a, "logistic_gate a")
+    _need(gate, "logistic_gate gate", a.dtype)
+    rows, width = a.shape
+    if gate.shape[0] != rows or gate_offset + width > gate.shape[1]:
+        raise KernelError(f"logistic_gate: shapes a {tuple(a.shape)}, gate {tuple(gate.shape)} from column {gate_offset}")
+    out = torch.empty_like(a)
+    _call("thn_logistic_gate", _ptr(out), _ptr(a), gate.data_ptr() + gate_offset * gate.element_size(), gate.shape[1],
+          rows, width, _code(a, "logistic_gate"), _stream())
+    return out
+
+
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
     _need(x, "rmsnorm x")
     _need(gain, "rmsnorm gain")
@@ -324,22 +362,33 @@ def clamped_glu(gu: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
     return out
 
 
+NORM_KINDS = {"rms": 1, "layer": 2, "as_is": 3}
+
+
 @dataclass
 class Gain:
-    """A norm's gain as the float32-residual kernels take it: ``weight`` float32 [width],
-    ``offset`` 0 for a gain stored as it multiplies and 1 for one stored around zero."""
+    """A norm as the float32-residual kernels take it: ``weight`` float32 [width], ``offset`` 0
+    for a gain stored as it multiplies and 1 for one stored around zero, ``eps``; ``kind`` "rms"
+    (``x / sqrt(mean(x^2) + eps)``) or "layer" (``(x - mean) / sqrt(var + eps)``, with an optional
+    ``bias`` float32 [width] added after the gain); "as_is" (as an output only): no norm, the
+    stream itself rounded to the activation type."""
 
-    weight: torch.Tensor
+    weight: Optional[torch.Tensor]
     offset: float
     eps: float
+    bias: Optional[torch.Tensor] = None
+    kind: str = "rms"
+
+
+STREAM_AS_IS = Gain(None, 0.0, 1.0, None, "as_is")
 
 
 def residual_norm(h: Optional[torch.Tensor], d: Optional[torch.Tensor], post: Optional[Gain], gain: Optional[Gain],
                   dtype: torch.dtype) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """Norms around a residual stream ``h`` kept in float32 beside activations of ``dtype``:
     ``h <- h + post(d)`` in place (``post`` None: ``d`` is added as it is; ``h`` None: the
-    stream starts as ``post(d)``), then ``y = gain(h)`` of ``dtype`` (``gain`` None: no y).
-    Both norms are ``x / sqrt(mean(x^2) + eps) * (offset + weight)``.  Returns ``(h, y)``."""
+    stream starts as ``post(d)``), then ``y = gain(h)`` of ``dtype`` (``gain`` None: no y;
+    ``STREAM_AS_IS``: y is h rounded).  See :class:`Gain` for the norms.  Returns ``(h, y)``."""
     if d is None and h is None:
         raise KernelError("residual_norm: neither a stream nor a branch")
     h_is_new = h is None
@@ -352,35 +401,43 @@ def residual_norm(h: Optional[torch.Tensor], d: Optional[torch.Tensor], post: Op
         raise KernelError(f"residual_norm: shapes h {tuple(h.shape)}, d {tuple(d.shape)}")
     width = h.shape[-1]
     rows = h.numel() // width
-    for g, what in ((post, "post gain"), (gain, "gain")):
-        if g is not None:
-            _need(g.weight, f"residual_norm {what}", torch.float32)
-            if g.weight.shape[0] != width:
-                raise KernelError(f"residual_norm: {what} has {g.weight.shape[0]} entries, rows have {width}")
+    if post is not None and post.kind == "as_is":
+        raise KernelError("residual_norm: 'as_is' is an output, not a norm of the branch")
+    for g, what in ((post, "post"), (gain, "gain")):
+        for t, name in (((g.weight, "gain"), (g.bias, "bias")) if g is not None else ()):
+            if t is not None:
+                _need(t, f"residual_norm {what} {name}", torch.float32)
+                if t.shape[0] != width:
+                    raise KernelError(f"residual_norm: {what} {name} has {t.shape[0]} entries, rows have {width}")
     y = torch.empty(h.shape, dtype=dtype, device=h.device) if gain is not None else None
     _call("thn_residual_norm", _ptr(y), _ptr(h), _ptr(d), _ptr(post.weight) if post else None,
-          float(post.offset) if post else 0.0, float(post.eps) if post else 1.0, _ptr(gain.weight) if gain else None,
-          float(gain.offset) if gain else 0.0, float(gain.eps) if gain else 1.0, rows, width, int(h_is_new),
-          DTYPE_CODE[dtype], _stream())
+          _ptr(post.bias) if post else None, float(post.offset) if post else 0.0, float(post.eps) if post else 1.0,
+          NORM_KINDS[post.kind] if post else 0, _ptr(gain.weight) if gain else None, _ptr(gain.bias) if gain else None,
+          float(gain.offset) if gain else 0.0, float(gain.eps) if gain else 1.0, NORM_KINDS[gain.kind] if gain else 0,
+          rows, width, int(h_is_new), DTYPE_CODE[dtype], _stream())
     return h, y
 
 
+GATE_KINDS = {"silu": 0, "logistic": 1}
+
+
 def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, gate_offset: int, weight: torch.Tensor, eps: float,
-                    n_heads: int, size: int, dtype: torch.dtype) -> torch.Tensor:
-    """o float32 [rows, heads, size] -> o / sqrt(mean over size + eps) * weight * silu(gate), of
+                    n_heads: int, size: int, dtype: torch.dtype, gate_kind: str = "silu") -> torch.Tensor:
+    """o float32 [rows, heads, size] -> o / sqrt(mean over size + eps) * weight * act(gate), of
     ``dtype`` [rows, heads * size]; the gate of a row is ``gate[row, gate_offset : gate_offset +
-    heads * size]``."""
+    heads * size]``; ``weight`` has ``size`` entries (shared by the heads) or ``heads * size``;
+    ``gate_kind`` "silu" or "logistic"."""
     _need(o, "gated_head_norm o", torch.float32)
     _need(gate, "gated_head_norm gate", dtype)
     _need(weight, "gated_head_norm weight", torch.float32)
     rows = o.shape[0]
-    if o.numel() != rows * n_heads * size or weight.shape[0] != size or gate.shape[0] != rows \
+    if o.numel() != rows * n_heads * size or weight.shape[0] not in (size, n_heads * size) or gate.shape[0] != rows \
             or gate_offset + n_heads * size > gate.shape[1]:
         raise KernelError(f"gated_head_norm: shapes o {tuple(o.shape)}, gate {tuple(gate.shape)}, weight {tuple(weight.shape)}")
     out = torch.empty((rows, n_heads * size), dtype=dtype, device=o.device)
     gate_ptr = gate.data_ptr() + gate_offset * gate.element_size()
     _call("thn_gated_head_norm", _ptr(out), _ptr(o), gate_ptr, gate.shape[1], _ptr(weight), float(eps), rows, n_heads,
-          size, DTYPE_CODE[dtype], _stream())
+          size, int(weight.shape[0] != size), GATE_KINDS[gate_kind], DTYPE_CODE[dtype], _stream())
     return out
 
 
@@ -544,6 +601,12 @@ class KVView:
     n_kv: int
     page_size: int
     head_dim: int
+    value_dim: Optional[int] = None   # size of a value where it differs from a key's (storage is then
+                                      # [pages, n_kv * page_size * (head_dim + value_dim)], K block then V block)
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass
@@ -602,12 +665,17 @@ def qk_norm_rope_cache(qkv, q_gain: Optional[torch.Tensor], k_gain: Optional[tor
 
 
 def attention_generic(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
-                      window: Optional[int], err: torch.Tensor, keep_first: int = 0) -> torch.Tensor:
+                      window: Optional[int], err: torch.Tensor, keep_first: int = 0, chunk: Optional[int] = None,
+                      exact_weights: bool = False) -> torch.Tensor:
+    """One warp per (row, head), any sizes.  ``chunk``: a row sees only the keys of its own chunk
+    of that many positions; ``exact_weights``: the softmax weights stay float32 where they
+    multiply the values; the output has ``kv.v_dim`` entries per head."""
     _need(q, "attention q")
-    out = torch.empty_like(q)
+    out = torch.empty((q.shape[0], n_q * kv.v_dim), dtype=q.dtype, device=q.device)
     _call("thn_attention_generic", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage),
-          _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, rows.n_rows, n_q,
-          float(scale), int(window or 0), int(keep_first or 0), _code(q, "attention"), _ptr(err), _stream())
+          _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, kv.v_dim, rows.n_rows, n_q,
+          float(scale), int(window or 0), int(keep_first or 0), int(chunk or 0), int(bool(exact_weights)),
+          _code(q, "attention"), _ptr(err), _stream())
     return out
 
 
@@ -637,31 +705,42 @@ def qk_prepare(proj: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optio
             raise KernelError(f"qk_prepare: gains of {q_gain.shape[0]} and {k_gain.shape[0]} entries, expected "
                               f"{want_q} and {want_k}")
     q = torch.empty((rows.n_rows, n_q * kv.head_dim), dtype=proj.dtype, device=proj.device)
+    if values_are_keys and kv.v_dim != kv.head_dim:
+        raise KernelError("qk_prepare: values that are the keys have the keys' size")
     _call("thn_qk_prepare", _ptr(q), _ptr(proj), proj.shape[1], _ptr(q_gain) if scope else None,
           _ptr(k_gain) if scope else None, scope, float(gain_offset), float(eps),
           _ptr(rotary.cos) if rotary else None, _ptr(rotary.sin) if rotary else None,
           rotary.cos.shape[0] if rotary else 0, rotary.rotary_dim if rotary else 0,
           ROTARY_LAYOUTS[rotary.layout] if rotary else 0, int(bool(values_are_keys)), _ptr(rows.row_slot),
           _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size,
-          kv.head_dim, rows.n_rows, n_q, int(bool(write_cache)), DTYPE_CODE[proj.dtype], _ptr(err), _stream())
+          kv.head_dim, kv.v_dim, rows.n_rows, n_q, int(bool(write_cache)), DTYPE_CODE[proj.dtype], _ptr(err), _stream())
     return q
 
 
-def prompt_attention_tile(dtype: torch.dtype, kv_head_dim: int, page_size: int, n_q: int, n_kv: int) -> int:
+def prompt_attention_tile(dtype: torch.dtype, kv_head_dim: int, page_size: int, n_q: int, n_kv: int,
+                          value_dim: Optional[int] = None, chunk: Optional[int] = None) -> int:
     """Rows per tile that the prompt attention kernel for these sizes works on, or 0 if the
     sizes go to the kernel that needs no tiles."""
+    if chunk or (value_dim is not None and value_dim != kv_head_dim):
+        return 0
     if dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv_head_dim, page_size, n_q, n_kv):
         return lib().thn_attention_prefill_tile_rows()
     return 0
 
 
 def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float, window: Optional[int],
-              err: torch.Tensor, tiles: Optional[RowTiles] = None, keep_first: int = 0) -> torch.Tensor:
+              err: torch.Tensor, tiles: Optional[RowTiles] = None, keep_first: int = 0,
+              chunk: Optional[int] = None, exact_weights: bool = False) -> torch.Tensor:
     """Causal attention of the step's rows over the cache (which already holds the step's
     own keys).  Chooses the kernel by dtype, head size and step shape; the tensor-core
     kernels for steps of several tokens per sequence need ``tiles``.  With a window,
-    ``keep_first`` keys at the start of a sequence stay visible to every later row."""
+    ``keep_first`` keys at the start of a sequence stay visible to every later row.  With
+    ``chunk`` a row sees the keys of its own chunk of that many positions only.
+    ``exact_weights`` asks for float32 softmax weights in the product with the values, which
+    the kernels without tensor cores honour."""
     keep_first = int(keep_first or 0) if window else 0
+    if chunk or kv.v_dim != kv.head_dim:
+        return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights)
     if q.dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
         if rows.max_q_len == 1:
             return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first)
@@ -669,7 +748,7 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
             if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
                 return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first)
             return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first)
-    return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first)
+    return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, exact_weights=exact_weights)
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
@@ -920,6 +999,145 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt
     return o
 
 
+# ------------------------------------------------------------------ latent attention
+
+
+def latent_norm(proj: torch.Tensor, offset: int, rank: int, gain: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMS norm of the ``rank`` entries from column ``offset`` of every projected row, times
+    ``gain`` (float32 [rank]) -> [rows, rank] of the rows' type: the latent that the
+    up-projection reads."""
+    _need(proj, "latent_norm proj")
+    _need(gain, "latent_norm gain", torch.float32)
+    if gain.shape[0] != rank or offset + rank > proj.shape[1]:
+        raise KernelError(f"latent_norm: {rank} entries from column {offset} of rows of {proj.shape[1]}, gain {tuple(gain.shape)}")
+    out = torch.empty((proj.shape[0], rank), dtype=proj.dtype, device=proj.device)
+    _call("thn_latent_norm", _ptr(out), proj.data_ptr() + offset * proj.element_size(), proj.shape[1], _ptr(gain),
+          float(eps), proj.shape[0], rank, _code(proj, "latent_norm"), _stream())
+    return out
+
+
+def latent_assemble(proj: torch.Tensor, q_offset: int, shared_offset: int, up: torch.Tensor,
+                    rotary: Optional[RotaryTables], rows: StepRows, kv: KVView, n_heads: int, plain: int, rot: int,
+                    err: torch.Tensor) -> torch.Tensor:
+    """Queries and cache entries of latent attention.  ``proj`` rows hold the queries
+    ``[heads][plain | rot]`` from column ``q_offset`` and one shared key part of ``rot`` entries
+    from column ``shared_offset``; ``up`` [rows, heads * plain + heads * value] is the
+    up-projection of the normalised latent.  The ``rot`` parts are rotated by the rows' positions
+    (interleaved pairs); the cache gets per head the key ``[plain | rotated shared part]`` and the
+    value.  Returns the queries [rows, heads * (plain + rot)]."""
+    _need(proj, "latent_assemble proj")
+    _need(up, "latent_assemble up", proj.dtype)
+    if kv.storage.dtype != proj.dtype or kv.n_kv != n_heads or kv.head_dim != plain + rot:
+        raise KernelError(f"latent_assemble: the cache entry ({kv.n_kv} heads of {kv.head_dim}, {kv.storage.dtype}) does "
+                          f"not fit {n_heads} heads of {plain} + {rot}, {proj.dtype}")
+    if proj.shape[0] != rows.n_rows or tuple(up.shape) != (rows.n_rows, n_heads * (plain + kv.v_dim)):
+        raise KernelError(f"latent_assemble: shapes proj {tuple(proj.shape)}, up {tuple(up.shape)} for {rows.n_rows} rows")
+    if rot and (rotary is None or rotary.layout != "interleaved" or rotary.rotary_dim != rot):
+        raise KernelError("latent_assemble: the rotated part needs interleaved tables of its size")
+    q = torch.empty((rows.n_rows, n_heads * (plain + rot)), dtype=proj.dtype, device=proj.device)
+    size = proj.element_size()
+    _call("thn_latent_assemble", _ptr(q), proj.data_ptr() + q_offset * size, proj.shape[1],
+          proj.data_ptr() + shared_offset * size, proj.shape[1], _ptr(up), _ptr(rotary.cos) if rot else None,
+          _ptr(rotary.sin) if rot else None, rotary.cos.shape[0] if rot else 0, _ptr(rows.row_slot), _ptr(rows.row_pos),
+          _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.page_size, rows.n_rows, n_heads, plain, rot,
+          kv.v_dim, _code(proj, "latent_assemble"), _ptr(err), _stream())
+    return q
+
+
+# ------------------------------------------------------------------ matrix memory (mLSTM)
+
+
+MLSTM_COLUMNS_PER_BLOCK = 16    # csrc/mlstm.cu: columns of a head's matrix per block (checked against the library)
+
+
+def mlstm_column_blocks(value_dim: int) -> int:
+    """Blocks of columns into which the recurrence kernel cuts a head's matrix; each keeps a
+    copy of the head's normaliser state."""
+    if lib().thn_mlstm_columns_per_block() != MLSTM_COLUMNS_PER_BLOCK:
+        raise KernelError("mlstm: the kernel library was built with another number of columns per block")
+    return -(-int(value_dim) // MLSTM_COLUMNS_PER_BLOCK)
+
+
+def mlstm(proj: torch.Tensor, gate_pre: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,
+          state: torch.Tensor, normaliser: torch.Tensor, rows: StepRows, n_heads: int, key_dim: int, value_dim: int,
+          q_scale: float, floor: float = 1e-6) -> torch.Tensor:
+    """The matrix-memory recurrence over a step's rows.  ``proj`` rows hold ``[q | k | v | ...]``
+    (heads * key_dim, heads * key_dim, heads * value_dim); ``gate_pre`` float32 [rows, 2 * heads]
+    the pre-activations of the input gates, then of the forget gates (biases are added here).
+    ``state`` float32 [slots, heads, value_dim, key_dim] and ``normaliser`` float32
+    [slots, heads, column blocks, key_dim + 1] (n, then m) are read and updated.  Returns the
+    read-out float32 [rows, heads, value_dim].  Single-token steps run as one kernel."""
+    _need(proj, "mlstm proj")
+    _need(gate_pre, "mlstm gates", torch.float32)
+    _need(bias_i, "mlstm bias", torch.float32)
+    _need(bias_f, "mlstm bias", torch.float32)
+    _need(state, "mlstm state", torch.float32)
+    _need(normaliser, "mlstm normaliser", torch.float32)
+    n = rows.n_rows
+    blocks = mlstm_column_blocks(value_dim)
+    if proj.shape[0] != n or tuple(gate_pre.shape) != (n, 2 * n_heads) or bias_i.shape[0] != n_heads \
+            or bias_f.shape[0] != n_heads or tuple(state.shape[1:]) != (n_heads, value_dim, key_dim) \
+            or tuple(normaliser.shape[1:]) != (n_heads, blocks, key_dim + 1) or normaliser.shape[0] != state.shape[0]:
+        raise KernelError(f"mlstm: shapes proj {tuple(proj.shape)}, gates {tuple(gate_pre.shape)}, state "
+                          f"{tuple(state.shape)}, normaliser {tuple(normaliser.shape)} do not fit {n_heads} heads of "
+                          f"{key_dim} x {value_dim}")
+    o = torch.empty((n, n_heads, value_dim), dtype=torch.float32, device=proj.device)
+    raw = rows.max_q_len == 1
+    gates = gate_pre
+    if not raw:
+        gates = torch.empty_like(gate_pre)
+        _call("thn_mlstm_gates", _ptr(gates), _ptr(gate_pre), _ptr(bias_i), _ptr(bias_f), float(cap), n, n_heads, _stream())
+    _call("thn_mlstm_recurrence", _ptr(o), _ptr(state), _ptr(normaliser), _ptr(proj), proj.shape[1], _ptr(gates),
+          _ptr(bias_i), _ptr(bias_f), float(cap), int(raw), _ptr(rows.cu_seqlens), _ptr(rows.slots), rows.n_seqs, n_heads,
+          key_dim, value_dim, float(q_scale), float(floor), _code(proj, "mlstm"), _stream())
+    return o
+
+
+# ------------------------------------------------------------------ mixture of experts
+
+
+@dataclass
+class Routing:
+    dense: torch.Tensor           # float32 [rows, experts]: the weight of every expert, 0 where not chosen
+    chosen: torch.Tensor          # int32 [rows, top]
+    chosen_weight: torch.Tensor   # float32 [rows, top]
+
+
+def moe_route(logits: torch.Tensor, n_experts: int, n_groups: int, keep: int, top: int, scale: float) -> Routing:
+    """Routing weights from float32 router logits (the first ``n_experts`` columns of
+    ``logits``): softmax over all experts, the ``keep`` best of ``n_groups`` groups of neighbours
+    (a group's score is its largest), the ``top`` best allowed experts, weights ``score * scale``."""
+    _need(logits, "moe_route logits", torch.float32)
+    rows = logits.shape[0]
+    if logits.shape[1] < n_experts:
+        raise KernelError(f"moe_route: rows of {logits.shape[1]} logits for {n_experts} experts")
+    dense = torch.empty((rows, n_experts), dtype=torch.float32, device=logits.device)
+    chosen = torch.empty((rows, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((rows, top), dtype=torch.float32, device=logits.device)
+    _call("thn_moe_route", _ptr(dense), _ptr(chosen), _ptr(weight), _ptr(logits), logits.shape[1], rows, n_experts,
+          n_groups, keep, top, float(scale), _stream())
+    return Routing(dense, chosen, weight)
+
+
+def routed_gelu(u: torch.Tensor, routing: Routing, ff: int, shared_ff: int,
+                shared_logit: Optional[torch.Tensor] = None, logit_column: int = 0) -> torch.Tensor:
+    """u [rows, experts * ff + shared_ff] -> gelu(u) (the exact one) times the routing weight of
+    the column's expert; the shared expert's columns times logistic(shared_logit[:, logit_column])
+    (no gate without ``shared_logit``)."""
+    _need(u, "routed_gelu u")
+    rows, n_experts = routing.dense.shape
+    if tuple(u.shape) != (rows, n_experts * ff + shared_ff):
+        raise KernelError(f"routed_gelu: u is {tuple(u.shape)}, expected {(rows, n_experts * ff + shared_ff)}")
+    logit_ptr, stride = None, 0
+    if shared_logit is not None:
+        _need(shared_logit, "routed_gelu gate logits", torch.float32)
+        logit_ptr, stride = shared_logit.data_ptr() + 4 * logit_column, shared_logit.shape[1]
+    out = torch.empty_like(u)
+    _call("thn_routed_gelu", _ptr(out), _ptr(u), _ptr(routing.dense), logit_ptr, stride, rows, n_experts, ff, shared_ff,
+          _code(u, "routed_gelu"), _stream())
+    return out
+
+
 # ------------------------------------------------------------------ token choice
 
 
@@ -963,5 +1181,5 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 __all__ = [
     "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "RowTiles", "StepRows", "row_tiles_of", "prompt_attention_tile", "linear_stream", "linear_swiglu", "linear_tcgen05", "add_rmsnorm", "advance",
     "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "attention_prefill_tcgen05", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
-    "qk_norm_rope_cache", "qk_prepare", "Gain", "residual_norm", "gated_head_norm", "clamped_glu", "DeltaShape", "delta_rule", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
+    "qk_norm_rope_cache", "qk_prepare", "Gain", "STREAM_AS_IS", "residual_norm", "gather_rows_scaled", "logistic_gate", "latent_norm", "latent_assemble", "mlstm", "mlstm_column_blocks", "Routing", "moe_route", "routed_gelu", "gated_head_norm", "clamped_glu", "DeltaShape", "delta_rule", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]

@@ -19,7 +19,13 @@ keys as projected, before norm and rotation: no ``v_proj``); ``keep_first`` 0 (w
 that many first positions of a sequence stay visible to every later query, at their own
 positions).  The position part's ``layout`` chooses the pairs of the rotation.  Anything but
 the defaults goes through :func:`ops.qk_prepare` (float32 inside, one rounding) instead of the
-per-head kernel.
+per-head kernel; ``prepare`` "float32" asks for that kernel with the defaults too.
+
+``value_dim`` (default ``head_dim``): the size of a head's value where it differs from its
+query's and key's.  ``chunk`` (instead of ``window``): position i sees j <= i only where
+``floor(i / chunk) = floor(j / chunk)``, chunks counted from the sequence's first position.
+``softmax_weights`` "float32": the weights stay float32 where they multiply the values, in
+the kernels that do not put that product on tensor cores.
 """
 
 from __future__ import annotations
@@ -42,11 +48,12 @@ class Attention:
     def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
         p = spec.params
         hidden, n_q, n_kv, d = int(p["hidden_size"]), int(p["n_heads"]), int(p["n_kv_heads"]), int(p["head_dim"])
+        dv = int(p.get("value_dim") or d)
         specs = [TensorSpec(spec.tensors["q_proj"], (n_q * d, hidden), MATRIX),
                  TensorSpec(spec.tensors["k_proj"], (n_kv * d, hidden), MATRIX)]
         if p.get("values", "projection") == "projection":
-            specs.append(TensorSpec(spec.tensors["v_proj"], (n_kv * d, hidden), MATRIX))
-        specs.append(TensorSpec(spec.tensors["o_proj"], (hidden, n_q * d), MATRIX))
+            specs.append(TensorSpec(spec.tensors["v_proj"], (n_kv * dv, hidden), MATRIX))
+        specs.append(TensorSpec(spec.tensors["o_proj"], (hidden, n_q * dv), MATRIX))
         if p.get("qk_norm_eps") is not None:
             whole = p.get("qk_norm_scope", "head") == "projection"
             specs += [TensorSpec(spec.tensors["q_norm"], (n_q * d if whole else d,), GAIN),
@@ -59,6 +66,11 @@ class Attention:
         if self.n_q % self.n_kv:
             raise ValueError(f"attention: {self.n_q} heads are not a multiple of {self.n_kv} kv heads")
         self.scale = float(p["scale"])
+        self.value_dim = int(p.get("value_dim") or self.head_dim)
+        self.chunk: Optional[int] = None if p.get("chunk") is None else int(p["chunk"])
+        if self.chunk is not None and (self.chunk <= 0 or p.get("window") is not None):
+            raise ValueError("attention: a chunk size is positive and stands instead of a window")
+        self.exact_weights = p.get("softmax_weights") == "float32"
         self.window: Optional[int] = None if p.get("window") is None else int(p["window"])
         self.eps = None if p.get("qk_norm_eps") is None else float(p["qk_norm_eps"])
         self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
@@ -66,6 +78,8 @@ class Attention:
         self.values_are_keys = p.get("values", "projection") == "keys"
         if self.norm_scope not in (None, "head", "projection") or p.get("values", "projection") not in ("projection", "keys"):
             raise ValueError(f"attention: qk_norm_scope {p.get('qk_norm_scope')!r} or values {p.get('values')!r} unknown")
+        if self.values_are_keys and self.value_dim != self.head_dim:
+            raise ValueError("attention: values that are the keys have the keys' size")
         projections = [runtime.tensor(spec, "q_proj"), runtime.tensor(spec, "k_proj")]
         if not self.values_are_keys:
             projections.append(runtime.tensor(spec, "v_proj"))
@@ -84,15 +98,17 @@ class Attention:
         # The per-head kernel (and the kernel that fuses it with single-token attention) takes the
         # defaults; every other variant is prepared by the general kernel.
         self.general = (self.norm_scope == "projection" or self.values_are_keys
+                        or p.get("prepare") == "float32" or self.value_dim != self.head_dim
                         or (self.position is not None and getattr(self.position, "layout", "half") != "half"))
         if self.general and self.eps is not None:
             self.q_gain, self.k_gain = self.q_gain.float().contiguous(), self.k_gain.float().contiguous()
 
     def cache_need(self) -> CacheNeed:
-        return KVSpec(self.n_kv, self.head_dim, self.window, self.keep_first)
+        return KVSpec(self.n_kv, self.head_dim, self.window, self.keep_first, self.chunk, self.value_dim)
 
     def _tile(self, page_size: int) -> int:
-        return ops.prompt_attention_tile(self.dtype, self.head_dim, page_size, self.n_q, self.n_kv)
+        return ops.prompt_attention_tile(self.dtype, self.head_dim, page_size, self.n_q, self.n_kv, self.value_dim,
+                                         self.chunk)
 
     def step_inputs(self, batch: HostBatch, out: Dict[str, List[int]]) -> None:
         """The prompt attention kernels work on tiles of consecutive rows of one sequence; the
@@ -112,7 +128,7 @@ class Attention:
             if row0 is not None:
                 tiles = ops.RowTiles(row0, ctx.inputs[f"row_tiles/{size}/rows"], row0.shape[0], size)
         qkv = ops.linear(x, self.w_qkv, err=ctx.err)
-        if self.general or self.keep_first:
+        if self.general or self.keep_first or self.chunk or self.exact_weights:
             rotary = self.position.tables() if self.position is not None else None
             if self.general:
                 q = ops.qk_prepare(qkv, self.q_gain, self.k_gain, self.norm_scope, self.eps or 1.0, rotary, ctx.rows, kv,
@@ -120,7 +136,8 @@ class Attention:
             else:
                 q = ops.qk_norm_rope_cache(qkv, self.q_gain, self.k_gain, self.eps if self.eps is not None else 1.0,
                                            rotary, ctx.rows, kv, self.n_q, entry.writes_cache, ctx.err)
-            a = ops.attention(q, ctx.rows, kv, self.n_q, self.scale, self.window, ctx.err, tiles, self.keep_first)
+            a = ops.attention(q, ctx.rows, kv, self.n_q, self.scale, self.window, ctx.err, tiles, self.keep_first,
+                              self.chunk, self.exact_weights)
             return ops.linear(a, self.w_o, err=ctx.err)
         a = ops.qkv_attention(qkv, self.q_gain, self.k_gain, self.eps if self.eps is not None else 1.0,
                               self.position.tables() if self.position is not None else None,

@@ -12,6 +12,11 @@ a new class of this family and nothing else.
 ``y = a + post'(ffn(norm'(a)))``, over a residual stream kept in float32; the feed-forward
 half may be absent.  The pending output travels as a :class:`Branch` that names the norm it
 still has to pass, so that this norm, the add and the next norm are one kernel.
+
+``branch_norm``: the norm stands on a sublayer's output only and the sublayers read the stream
+itself: ``a = x + norm(mixer(x))``, ``y = a + norm'(ffn(a))``, over a float32 stream; the
+feed-forward half may be absent.  The pending output again travels as a :class:`Branch`, and
+"norm of the branch, add, round the sum for the next sublayer" is one kernel.
 """
 
 from __future__ import annotations
@@ -99,3 +104,23 @@ class SandwichNormBlock(Block):
             return h, a
         n = self.norm_ffn.add_forward(h, a.tensor, post=a.norm)
         return h, Branch(self.ffn.forward(n, ctx), self.post_norm_ffn)
+
+
+@register_part("block", "branch_norm")
+class BranchNormBlock(Block):
+    MEMBERS = {"mixer": "mixer", "norm_mixer": "norm", "ffn": "ffn", "norm_ffn": "norm"}
+
+    def forward(self, h: torch.Tensor, d, ctx: StepContext, entry: ScheduleEntry):
+        if h.dtype != torch.float32:
+            raise TypeError("branch_norm: the residual stream must start in float32 (an embedding with stream 'float32')")
+        if d is None:
+            x = self.norm_mixer.read(h)
+        elif isinstance(d, Branch) and d.norm is not None:
+            x = d.norm.add_read(h, d.tensor)
+        else:
+            raise TypeError("branch_norm: a pending branch must name the norm it passes before the add")
+        a = Branch(self.mixer.forward(x, ctx, entry), self.norm_mixer)
+        if self.ffn is None:
+            return h, a
+        x = self.norm_mixer.add_read(h, a.tensor)
+        return h, Branch(self.ffn.forward(x, ctx), self.norm_ffn)

@@ -1,6 +1,10 @@
 """Token embedding (a row gather, engine/engine.py:1101) and the LM head
 (engine/engine.py:1120; with tied weights it is the embedding table, :225-226).
-Logits are float32."""
+Logits are float32.
+
+The embedding takes two optional parameters: ``scale`` (the rows are multiplied by it) and
+``stream`` "float32" (the rows come out in float32, scaled in float32: the start of a residual
+stream that is kept in float32)."""
 
 from __future__ import annotations
 
@@ -24,8 +28,14 @@ class Embedding:
 
     def __init__(self, spec: PartSpec, runtime: Runtime):
         self.table = runtime.tensor(spec, "weight")
+        self.scale = float(spec.params.get("scale", 1.0))
+        self.float32_stream = spec.params.get("stream") == "float32"
+        if self.scale != 1.0 and not self.float32_stream:
+            raise ValueError("embedding: a scale needs stream 'float32'")
 
     def forward(self, tokens: torch.Tensor, err: torch.Tensor) -> torch.Tensor:
+        if self.float32_stream:
+            return ops.gather_rows_scaled(self.table, tokens, self.scale, err)
         return ops.gather_rows(self.table, tokens, err)
 
 

@@ -3,7 +3,19 @@ are one product over the concatenated weight ``[2I, H]`` (engine/engine.py:221, 
 the activation rounds as engine/kernels/torch_ref.py:74-88 does.
 
 ``clamped_glu``: ``down(g * logistic(slope * g) * (u + 1))`` with ``g = min(gate(x), limit)`` and
-``u = clamp(up(x), -limit, limit)``; ``limit`` and ``slope`` are parameters."""
+``u = clamp(up(x), -limit, limit)``; ``limit`` and ``slope`` are parameters.
+
+``routed_experts``: a mixture of ``n_experts`` experts ``down_e(gelu(up_e(x)))`` (the exact gelu,
+no biases) of which a token uses ``top``.  Router logits ``z = router(x)`` and scores
+``s = softmax(z)`` over all experts are float32; the experts form ``groups`` equal groups of
+neighbours, a group's score is its largest ``s``, only experts of the ``keep`` best groups can be
+chosen, and the chosen are the ``top`` allowed experts with the largest ``s``; a chosen expert's
+output is weighted by ``s * scale`` (not renormalised).  With ``shared_ff`` a shared expert of
+the same form runs for every token and is added, multiplied by ``logistic(shared_gate(x))`` (one
+number per token; ``shared_gated`` False: added as it is).  The up-projections of all experts are
+one product, the activation carries the routing weights (zero for an expert that was not chosen),
+and one down-projection over all experts' columns sums the chosen ones: the result does not
+depend on the other rows of the step.  Kernels: csrc/moe.cu."""
 
 from __future__ import annotations
 
@@ -51,3 +63,55 @@ class ClampedGLU:
         err = getattr(ctx, "err", None)
         y = ops.clamped_glu(ops.linear(x, self.w_gate_up, err=err), self.limit, self.slope)
         return ops.linear(y, self.w_down, err=err)
+
+
+@register_part("ffn", "routed_experts")
+class RoutedExperts:
+    @staticmethod
+    def _sizes(spec: PartSpec):
+        p = spec.params
+        return int(p["hidden_size"]), int(p["n_experts"]), int(p["expert_ff"]), int(p.get("shared_ff") or 0)
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
+        hidden, n, ff, shared = cls._sizes(spec)
+        specs = [TensorSpec(spec.tensors["router"], (n, hidden), MATRIX)]
+        for e in range(n):
+            specs += [TensorSpec(spec.tensors[f"up.{e}"], (ff, hidden), MATRIX),
+                      TensorSpec(spec.tensors[f"down.{e}"], (hidden, ff), MATRIX)]
+        if shared:
+            specs += [TensorSpec(spec.tensors["shared_up"], (shared, hidden), MATRIX),
+                      TensorSpec(spec.tensors["shared_down"], (hidden, shared), MATRIX)]
+            if spec.params.get("shared_gated", True):
+                specs.append(TensorSpec(spec.tensors["shared_gate"], (1, hidden), MATRIX))
+        return specs
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        p = spec.params
+        _, self.n_experts, self.ff, self.shared_ff = self._sizes(spec)
+        self.top, self.scale = int(p["top"]), float(p.get("scale", 1.0))
+        self.groups, self.keep = int(p.get("groups") or 1), int(p.get("keep") or p.get("groups") or 1)
+        if self.n_experts % self.groups or not 0 < self.keep <= self.groups \
+                or not 0 < self.top <= self.keep * (self.n_experts // self.groups):
+            raise ValueError(f"routed_experts: top {self.top} of {self.n_experts} experts in {self.groups} groups, "
+                             f"{self.keep} kept")
+        self.shared_gated = bool(self.shared_ff) and bool(p.get("shared_gated", True))
+        ups = [runtime.tensor(spec, f"up.{e}") for e in range(self.n_experts)]
+        downs = [runtime.tensor(spec, f"down.{e}") for e in range(self.n_experts)]
+        route = [runtime.tensor(spec, "router")]
+        if self.shared_ff:
+            ups.append(runtime.tensor(spec, "shared_up"))
+            downs.append(runtime.tensor(spec, "shared_down"))
+        if self.shared_gated:
+            route.append(runtime.tensor(spec, "shared_gate"))
+        self.w_up = torch.cat(ups, dim=0).contiguous()
+        self.w_down = torch.cat(downs, dim=1).contiguous()
+        self.w_route = torch.cat(route, dim=0).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        err = getattr(ctx, "err", None)
+        z = ops.linear(x, self.w_route, out_dtype=torch.float32, err=err)
+        routing = ops.moe_route(z, self.n_experts, self.groups, self.keep, self.top, self.scale)
+        u = ops.linear(x, self.w_up, err=err)
+        a = ops.routed_gelu(u, routing, self.ff, self.shared_ff, z if self.shared_gated else None, self.n_experts)
+        return ops.linear(a, self.w_down, err=err)

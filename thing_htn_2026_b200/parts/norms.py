@@ -7,7 +7,13 @@ which multiplies as ``1 + w``); ``residual`` (default: the activation type; "flo
 stream this norm reads is kept in float32 whatever the activation type, and every sum of the
 norm is float32 with one rounding at the output).  With a float32 stream, ``add_forward``
 also takes ``post``: another norm of this kind that the branch's output passes before it is
-added (norms on both sides of a sublayer), in the same kernel."""
+added (norms on both sides of a sublayer), in the same kernel.
+
+``layernorm``: ``(x - mean) / sqrt(var + eps) * w + b`` with the variance as the mean of the
+squared deviations, over a float32 stream only.  Besides the calls above it has ``read`` and
+``add_read`` for arrangements whose sublayers read the stream itself, with the norm on a
+sublayer's output: ``add_read(h, d)`` does ``h <- h + self(d)`` and returns ``h`` rounded to the
+activation type, in one kernel."""
 
 from __future__ import annotations
 
@@ -62,3 +68,40 @@ class RMSNorm:
         """``h <- h + self(d)`` on a float32 stream, nothing else: this norm as the one a branch
         passes before the add, with no norm of the sum wanted."""
         ops.residual_norm(h, d, self.as_gain, None, self.dtype)
+
+
+@register_part("norm", "layernorm")
+class LayerNorm:
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
+        size = int(spec.params["size"])
+        specs = [TensorSpec(spec.tensors["weight"], (size,), GAIN)]
+        if "bias" in spec.tensors:
+            specs.append(TensorSpec(spec.tensors["bias"], (size,), GAIN, init="small_normal"))
+        return specs
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        if spec.params.get("residual") != "float32":
+            raise ValueError("layernorm: this norm works on a residual stream kept in float32 (residual: 'float32')")
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.dtype = runtime.dtype
+        bias = runtime.tensor(spec, "bias").to(torch.float32).contiguous() if "bias" in spec.tensors else None
+        self.as_gain = ops.Gain(runtime.tensor(spec, "weight").to(torch.float32).contiguous(), 0.0, self.eps, bias, "layer")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.residual_norm(x, None, None, self.as_gain, self.dtype)[1]
+
+    def add_forward(self, h: torch.Tensor, d: torch.Tensor, post=None) -> torch.Tensor:
+        return ops.residual_norm(h, d, post.as_gain if post is not None else None, self.as_gain, self.dtype)[1]
+
+    def add_only(self, h: torch.Tensor, d: torch.Tensor) -> None:
+        ops.residual_norm(h, d, self.as_gain, None, self.dtype)
+
+    def read(self, h: torch.Tensor) -> torch.Tensor:
+        """The stream rounded to the activation type: what a sublayer that reads the stream itself gets."""
+        return ops.residual_norm(h, None, None, ops.STREAM_AS_IS, self.dtype)[1]
+
+    def add_read(self, h: torch.Tensor, d: torch.Tensor) -> torch.Tensor:
+        """``h <- h + self(d)``; returns the new stream rounded to the activation type."""
+        return ops.residual_norm(h, d, self.as_gain, ops.STREAM_AS_IS, self.dtype)[1]

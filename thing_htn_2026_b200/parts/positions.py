@@ -10,10 +10,19 @@ its tables the same way, engine/engine.py:232-251).
 ``layout`` says which entries of a head make a pair: "half" (entry i with entry
 i + rotary_dim / 2, the default) or "interleaved" (entry 2i with entry 2i + 1).
 ``frequency_precision`` "float64" computes ``inv_freq`` in double precision before it is
-rounded to float32 (one rounding instead of the float32 expression's several)."""
+rounded to float32 (one rounding instead of the float32 expression's several).
+
+``scaling`` (a mapping ``factor, original, fast, slow``) stretches the slow pairs for sequences
+longer than ``original`` positions (YaRN).  With ``turn(t) = rotary_dim * ln(original / (2 pi t))
+/ (2 ln theta)``, the pair index whose wavelength fits ``original`` positions t times,
+``lo = max(floor(turn(fast)), 0)``, ``hi = min(ceil(turn(slow)), rotary_dim - 1)`` and
+``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, pair i turns with
+``inv_freq[i] / factor * ramp_i + inv_freq[i] * (1 - ramp_i)``, and cos and sin are both
+multiplied by ``0.1 ln(factor) + 1`` (the tables carry that magnitude)."""
 
 from __future__ import annotations
 
+import math
 from typing import List
 
 import torch
@@ -46,6 +55,22 @@ class Rope:
         else:
             exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).to(torch.float32) / self.rotary_dim
             self.inv_freq = (1.0 / (self.theta ** exponent)).to(runtime.device)
+        self.magnitude = 1.0
+        scaling = spec.params.get("scaling")
+        if scaling:
+            factor, original = float(scaling["factor"]), float(scaling["original"])
+            exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).to(torch.float64) / self.rotary_dim
+            plain = self.theta ** -exponent
+
+            def turn(t: float) -> float:
+                return self.rotary_dim * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(turn(float(scaling["fast"]))), 0)
+            hi = min(math.ceil(turn(float(scaling["slow"]))), self.rotary_dim - 1)
+            index = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+            ramp = ((index - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            self.inv_freq = (plain / factor * ramp + plain * (1.0 - ramp)).to(torch.float32).to(runtime.device)
+            self.magnitude = 0.1 * math.log(factor) + 1.0
         self.device = runtime.device
         self._tables = None
 
@@ -59,6 +84,9 @@ class Rope:
         cos = torch.empty((size, half), dtype=torch.float32, device=self.device)
         sin = torch.empty((size, half), dtype=torch.float32, device=self.device)
         ops.rope_table(cos, sin, self.inv_freq, 0, size)
+        if self.magnitude != 1.0:
+            cos.mul_(self.magnitude)
+            sin.mul_(self.magnitude)
         self._tables = ops.RotaryTables(cos, sin, self.rotary_dim, self.layout)
 
     def tables(self) -> ops.RotaryTables:

@@ -59,11 +59,21 @@ def _unit_normal(t, generator, matrix_std, gain_std):
     return t.normal_(0.0, 1.0, generator=generator)
 
 
+def _small_normal(t, generator, matrix_std, gain_std):
+    """A bias: around zero, of the order of a gain's spread."""
+    return t.normal_(0.0, gain_std, generator=generator)
+
+
+def _gate_bias(t, generator, matrix_std, gain_std):
+    """Bias of a gate's pre-activation: between -2 and 5, so that gates open, shut and saturate."""
+    return t.uniform_(0.0, 1.0, generator=generator).mul_(7.0).sub_(2.0)
+
+
 # How a tensor is drawn, by the name in ``TensorSpec.init``.  ``fill(t, generator, matrix_std,
 # gain_std)`` fills ``t`` (float32 on the CPU, the held dtype on a device) in place.
 INITIALIZERS: Dict[str, Callable] = {"normal": _normal, "one_plus_normal": _one_plus_normal, "zeros": _zeros,
                                      "zero_centered": _zero_centered, "conv_taps": _conv_taps, "log_rate": _log_rate,
-                                     "unit_normal": _unit_normal}
+                                     "unit_normal": _unit_normal, "small_normal": _small_normal, "gate_bias": _gate_bias}
 # The rule of a spec that names none, by its role.
 ROLE_INIT = {MATRIX: "normal", GAIN: "one_plus_normal", TABLE: "zeros"}
 
