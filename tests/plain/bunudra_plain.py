@@ -70,7 +70,7 @@ class Arithmetic:
         return t.to(torch.bfloat16).to(self.work) if self.round_products else t
 
     def linear(self, x, w, keep=False):
-        """w is stored [out, in] and applied as w x; ``keep``: the result is not rounded."""
+        """``x @ w.T`` for a weight matrix of shape [outputs, inputs]; ``keep``: the result is not rounded."""
         y = self.rb(x) @ self.rb(w.to(self.work)).t()
         return y if keep else self.rb(y)
 

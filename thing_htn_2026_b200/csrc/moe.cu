@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
     __syncwarp();
     // the `keep` best groups stay as they are; the scores of the others are hidden behind a sign
     if (keep < n_groups) {
-        for (int round = 0; round < keep; ++round) {
+        for (int pick = 0; pick < keep; ++pick) {
             Best b{-1.f, 0x7fffffff};
             for (int g = lane; g < n_groups; g += 32)
                 if (group_score[g] > b.value) { b.value = group_score[g]; b.index = g; }
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
             if (group_score[e / per] != -2.f) s[e] = -1.f - s[e];      // not allowed; the score is kept, negative
         __syncwarp();
     }
-    for (int round = 0; round < top; ++round) {
+    for (int pick = 0; pick < top; ++pick) {
         Best b{-1.f, 0x7fffffff};
         for (int e = lane; e < n_experts; e += 32)
             if (s[e] > b.value) { b.value = s[e]; b.index = e; }
@@ -94,8 +94,8 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
         if (lane == 0) {
             const float w = b.value * scale;
             dense[(size_t)row * n_experts + b.index] = w;
-            chosen[(size_t)row * top + round] = b.index;
-            chosen_weight[(size_t)row * top + round] = w;
+            chosen[(size_t)row * top + pick] = b.index;
+            chosen_weight[(size_t)row * top + pick] = w;
             s[b.index] = -4.f;       // taken
         }
         __syncwarp();
