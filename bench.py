@@ -25,7 +25,10 @@ Qwen3-14B sizes.
 windowed-attention layer) beside a Qwen3 decoder of the same width, feed-forward, heads, head
 size, depth and vocabulary: prefill of one 2,048-token prompt and decode steps at ``--batch``,
 and every kernel of the new design alone (cold caches) beside the like kernel of the Qwen3
-path, each with the fraction of its roofline.  The default run is untouched by it.
+path, each with the fraction of its roofline.  ``--design bunudra`` does the same for the Bunudra
+decoder (``bunudra-w2048``, ``bunudra-w4096``: matrix-memory, chunked-attention and
+latent-attention layers with routed experts) beside a Lanilix decoder of the same width, depth,
+heads and feed-forward weights, its closest relative here.  The default run is untouched by both.
 """
 
 from __future__ import annotations
@@ -652,6 +655,230 @@ def kernel_table(torch, lan, peak, batch, context):
     return rows
 
 
+BUNUDRA_SIZES = ("bunudra-w2048", "bunudra-w4096")
+
+
+def lanilix_like(bun):
+    """A Lanilix config.json of the same width, depth, vocabulary, head counts and sizes as a
+    Bunudra configuration: a gated-delta-rule layer for every matrix-memory layer, a windowed
+    attention (window = the chunk or window size, four kept positions) for every attention layer,
+    and a dense gated feed-forward with as many weights as all experts together."""
+    attn = next(l for l in bun["layers"] if l["type"] == "attention")["mixer"]
+    layers = []
+    for layer in bun["layers"]:
+        m, mlp = layer["mixer"], layer["mlp"]
+        ff = (mlp["router"]["experts"] * mlp["expert"]["ff"] + mlp["shared"]["ff"]) * 2 // 3
+        if layer["type"] == "mlstm":
+            mixer = {"heads": m["heads"], "kv_heads": attn["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "conv": 4}
+            kind = "delta"
+        else:
+            mixer = {"heads": m["heads"], "kv_heads": attn["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                     "rot": {"dims": 64, "base": 1000000.0}, "mask": {"size": m["mask"]["size"], "keep_first": 4}}
+            kind = "attention"
+        layers.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}})
+    return {"architecture": "Lanilix", "vocab": bun["vocab"], "width": bun["width"], "norm": bun["norm"], "layers": layers}
+
+
+def bunudra_kernel_table(torch, bun, peak, batch, context):
+    """Every kernel of the Bunudra design alone, beside the like kernel of the Lanilix path, cold
+    caches (a buffer larger than L2 is written between timed launches): microseconds, and the
+    fraction of the roofline that the kernel's algorithmic bytes or flops amount to."""
+    from thing_htn_2026_b200 import ops
+    from thing_htn_2026_b200.cache import KVSpec, SequenceCache, StateSpec
+    dev, bf = "cuda:0", torch.bfloat16
+    attn = next(l for l in bun["layers"] if l["type"] == "attention")["mixer"]
+    mem = next(l for l in bun["layers"] if l["type"] == "mlstm")["mixer"]
+    lat = next(l for l in bun["layers"] if l["type"] == "latent_attention")["mixer"]
+    mlp = bun["layers"][0]["mlp"]
+    W, T = bun["width"], PREFILL_TOKENS
+    E, ff, sff, top = mlp["router"]["experts"], mlp["expert"]["ff"], mlp["shared"]["ff"], mlp["router"]["top"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    hbm, tensor = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12
+
+    def timed(fn, reps=7):
+        out = []
+        for _ in range(reps):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            out.append(start.elapsed_time(end) * 1e3)
+        return statistics.median(out[2:])
+
+    rows = {}
+
+    def row(name, fn, nbytes=0, flops=0, flop_peak=None, like=None):
+        us = timed(fn)
+        t_roof = max(nbytes / hbm, flops / (flop_peak or tensor)) * 1e6
+        rows[name] = {"us": round(us, 2), "roofline_us": round(t_roof, 2), "frac": round(t_roof / us, 3), "like": like,
+                      "bound": "hbm" if nbytes / hbm >= flops / (flop_peak or tensor) else "flops"}
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev)
+    err = ops.new_error_word(dev)
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        # ---- norms: layer norm of the branch, add, the sum rounded; against two RMS norms around the add
+        h32, d16 = rnd(n, W), rnd(n, W).to(bf)
+        layer = ops.Gain(1 + rnd(W) * 0.1, 0.0, 1e-6, rnd(W) * 0.1, "layer")
+        rms = ops.Gain(rnd(W) * 0.1, 1.0, 1e-6)
+        row(f"{tag}: residual_norm (layer norm of the branch, add, the sum as it is)",
+            lambda: ops.residual_norm(h32, d16, layer, ops.STREAM_AS_IS, bf), nbytes=n * W * (4 + 4 + 2 + 2),
+            like=f"{tag}: residual_norm (two RMS norms)")
+        row(f"{tag}: residual_norm (two RMS norms)", lambda: ops.residual_norm(h32, d16, rms, rms, bf),
+            nbytes=n * W * (4 + 4 + 2 + 2))
+        # ---- the experts' activation with the routing weights, against the clamped gated unit
+        z = rnd(n, E + 1)
+        routing = ops.moe_route(z, E, mlp["router"]["groups"]["count"], mlp["router"]["groups"]["keep"], top, 2.0)
+        u = rnd(n, E * ff + sff).to(bf)
+        gu = rnd(n, 2 * (E * ff + sff) * 2 // 3 // 2 * 2).to(bf)
+        row(f"{tag}: moe_route", lambda: ops.moe_route(z, E, mlp["router"]["groups"]["count"],
+                                                        mlp["router"]["groups"]["keep"], top, 2.0),
+            nbytes=n * ((E + 1) * 4 + E * 4 + top * 8))
+        row(f"{tag}: routed_gelu", lambda: ops.routed_gelu(u, routing, ff, sff, z, E),
+            nbytes=n * ((top * ff + sff) * 2 + (E * ff + sff) * 2), like=f"{tag}: clamped_glu")
+        row(f"{tag}: clamped_glu", lambda: ops.clamped_glu(gu, 7.0, 1.702), nbytes=n * gu.shape[1] * 3)
+        # ---- the output gate of latent attention, against the same
+        Hl, El = lat["heads"], lat["vdim"]
+        a16, g16 = rnd(n, Hl * El).to(bf), rnd(n, Hl * El + 64).to(bf)
+        row(f"{tag}: logistic_gate", lambda: ops.logistic_gate(a16, g16, 64), nbytes=n * Hl * El * 6, like=f"{tag}: clamped_glu")
+
+    # ---- attention over a paged cache: one sequence of T tokens, then `batch` sequences at `context` keys
+    def attention_rows(tag, spec, H, prepare_of, chunk, window, keep, likes):
+        n_slots = batch + 1
+        cache = SequenceCache([spec], max_tokens=(batch * (context + 64) + T + 64), dtype=bf, device=dev, max_slots=n_slots + 1)
+        slots = cache.open(n_slots)
+        D, G = spec.head_dim, spec.n_kv
+
+        def step_of(slot_list, counts):
+            cache.prepare(slot_list, counts)
+            cu = [0]
+            for c in counts:
+                cu.append(cu[-1] + c)
+            cu_dev = torch.tensor(cu, dtype=torch.int32, device=dev)
+            slots_dev = torch.tensor(slot_list, dtype=torch.int32, device=dev)
+            rows_ = ops.step_rows(cu_dev, slots_dev, cache.seq_lens, cu[-1], max(counts),
+                                  max_context=max(cache.length(s) + c for s, c in zip(slot_list, counts)),
+                                  lengths_differ=False)
+            return rows_, cu_dev, slots_dev
+
+        rows_, cu_dev, slots_dev = step_of([slots[0]], [T])
+        prepare, prep_bytes = prepare_of(cache, T)
+        size = ops.prompt_attention_tile(bf, D, cache.page_size, H, G)
+        r0, rn = ops.row_tiles_of([T], [0], size)
+        tiles = ops.RowTiles(torch.tensor(r0, dtype=torch.int32, device=dev), torch.tensor(rn, dtype=torch.int32, device=dev),
+                             len(r0), size)
+        first = lambda i: i // chunk * chunk if chunk else max(0, i - (window or T) + 1)
+        seen = sum(i - first(i) + 1 + (min(keep, first(i)) if window else 0) for i in range(T))
+        row(f"prefill: {tag[0]}", lambda: prepare(rows_), nbytes=prep_bytes(T), like=likes[0])
+        q = prepare(rows_)
+        row(f"prefill: {tag[1]}", lambda: ops.attention(q, rows_, cache.kv_view(0), H, D ** -0.5, window, err, tiles, keep, chunk),
+            flops=4.0 * H * D * seen, nbytes=T * H * D * 4, like=likes[1])
+        others = slots[1:]
+        rows_, cu_dev, slots_dev = step_of(others, [context] * batch)
+        prepare_c, _ = prepare_of(cache, batch * context)
+        prepare_c(rows_)
+        ops.advance(cache.seq_lens, slots_dev, cu_dev)
+        cache.commit(others, [context] * batch)
+        rows_, cu_dev, slots_dev = step_of(others, [1] * batch)
+        prepare_1, _ = prepare_of(cache, batch)
+        row(f"decode: {tag[0]}", lambda: prepare_1(rows_), nbytes=prep_bytes(batch), like=likes[2])
+        q1 = prepare_1(rows_)
+        keys = context + 1 - first(context) + (min(keep, first(context)) if window else 0)
+        row(f"decode: {tag[1]}", lambda: ops.attention(q1, rows_, cache.kv_view(0), H, D ** -0.5, window, err, None, keep, chunk),
+            nbytes=batch * G * keys * D * 2 * 2, like=likes[3])
+
+    H, G, D = attn["heads"], attn["kv_heads"], attn["dim"]
+    size = attn["mask"]["size"]
+    half_tables = ops.RotaryTables(torch.ones(8192, attn["rot"]["dims"] // 2, device=dev),
+                                   torch.zeros(8192, attn["rot"]["dims"] // 2, device=dev), attn["rot"]["dims"], "half")
+    pair_tables = ops.RotaryTables(torch.ones(8192, D // 4, device=dev), torch.zeros(8192, D // 4, device=dev), D // 2, "interleaved")
+
+    def head_norm_prepare(cache, n):          # Bunudra: norm per head, rotate-half on the first entries, values of their own
+        proj = rnd(n, (H + 2 * G) * D).to(bf)
+        qg, kg = 1 + rnd(D) * 0.1, 1 + rnd(D) * 0.1
+        return (lambda rows_: ops.qk_prepare(proj, qg, kg, "head", 1e-6, half_tables, rows_, cache.kv_view(0), H, False, True, err),
+                lambda m: m * ((H + 2 * G) * D * 2 + (H + 2 * G) * D * 2))
+
+    def whole_norm_prepare(cache, n):         # Lanilix: norm over the projection, interleaved pairs, values are the keys
+        proj = rnd(n, (H + G) * D).to(bf)
+        qg, kg = 1 + rnd(H * D) * 0.1, 1 + rnd(G * D) * 0.1
+        return (lambda rows_: ops.qk_prepare(proj, qg, kg, "projection", 1e-6, pair_tables, rows_, cache.kv_view(0), H, True, True, err),
+                lambda m: m * ((H + G) * D * 2 + (H + 2 * G) * D * 2))
+
+    lanilix_tags = ("qk_prepare (Lanilix attention)", f"attention (window {size} + 4 kept)")
+    attention_rows(lanilix_tags, KVSpec(G, D, size, 4), H, whole_norm_prepare, None, size, 4, (None,) * 4)
+    likes = tuple(f"{t}: {x}" for t in ("prefill", "decode") for x in lanilix_tags)
+    likes = (likes[0], likes[1], likes[2], likes[3])
+    attention_rows(("qk_prepare (head norm, rotate-half)", f"attention (chunks of {size})"), KVSpec(G, D, None, 0, size), H,
+                   head_norm_prepare, size, None, 0, likes)
+
+    Hl, P, R, El, C = lat["heads"], lat["dim"], lat["rot_dim"], lat["vdim"], lat["kv_rank"]
+    lat_tables = ops.RotaryTables(torch.ones(8192, R // 2, device=dev), torch.zeros(8192, R // 2, device=dev), R, "interleaved")
+
+    def latent_prepare(cache, n):
+        width = Hl * (P + R) + C + R + Hl * El
+        proj = rnd(n, width).to(bf)
+        up = rnd(n, Hl * (P + El)).to(bf)
+        gain = 1 + rnd(C) * 0.1
+
+        def run(rows_):
+            ops.latent_norm(proj, Hl * (P + R), C, gain, 1e-6)
+            return ops.latent_assemble(proj, 0, Hl * (P + R) + C, up, lat_tables, rows_, cache.kv_view(0), Hl, P, R, err)
+        return run, lambda m: m * ((Hl * (P + R) + 2 * C + R + Hl * (P + El)) * 2 + (Hl * (P + R) + Hl * (P + R + El)) * 2)
+
+    attention_rows(("latent_norm + latent_assemble", f"attention (latent heads, window {lat['mask']['size']})"),
+                   KVSpec(Hl, P + R, lat["mask"]["size"], 0, None, El), Hl, latent_prepare, None, lat["mask"]["size"], 0, likes)
+
+    # ---- the matrix memory against the delta rule: a prompt of T tokens, a step of `batch` sequences, `batch` prompts
+    Hm, dk, dv = mem["heads"], mem["dim"], mem["vdim"]
+    blocks = ops.mlstm_column_blocks(dv)
+    cache = SequenceCache([(StateSpec((Hm, dv, dk), torch.float32), StateSpec((Hm, blocks, dk + 1), torch.float32))],
+                          max_tokens=64 * (batch + 2), dtype=bf, device=dev, max_slots=batch + 2)
+    slots = cache.open(batch + 1)
+    bias_i, bias_f = rnd(Hm) - 2.0, rnd(Hm) + 3.0
+    shape = ops.DeltaShape(Hm, attn["kv_heads"], dk, dv, 4)
+    dcache = SequenceCache([(StateSpec((Hm, dv, dk), torch.float32), StateSpec((shape.taps, shape.conv_channels), bf))],
+                           max_tokens=64 * (batch + 2), dtype=bf, device=dev, max_slots=batch + 2)
+    dslots = dcache.open(batch + 1)
+    conv_w, a_log, dt_bias = rnd(shape.conv_channels, shape.taps) * 0.5, rnd(Hm) - 3.0, rnd(Hm)
+    for n, pick, tag in ((T, slice(0, 1), "prefill"), (1, slice(1, None), "decode"), (T, slice(1, None), f"prefill of {batch} prompts")):
+        who, dwho = slots[pick], dslots[pick]
+        cu = torch.arange(len(who) + 1, dtype=torch.int32, device=dev) * n
+        tokens = n * len(who)
+        rows_ = ops.step_rows(cu, torch.tensor(who, dtype=torch.int32, device=dev), cache.seq_lens, tokens, n)
+        drows = ops.step_rows(cu, torch.tensor(dwho, dtype=torch.int32, device=dev), dcache.seq_lens, tokens, n)
+        proj = (rnd(tokens, Hm * (2 * dk + 2 * dv)) * 0.5).to(bf)
+        pre = rnd(tokens, 2 * Hm)
+        dproj = rnd(tokens, shape.proj_width).to(bf)
+        state_bytes = len(who) * Hm * dk * dv * 4 * 2
+        row(f"{tag}: delta_rule (conv, norms, recurrence)",
+            lambda: ops.delta_rule(dproj, conv_w, a_log, dt_bias, dcache.state_view(0, 0), dcache.state_view(0, 1), drows,
+                                   dcache.seq_lens, shape, 1e-6),
+            nbytes=state_bytes + tokens * (shape.proj_width * 2 + Hm * dv * 4), flops=6.0 * tokens * Hm * dk * dv,
+            flop_peak=FP32_CORE_TFLOPS * 1e12)
+        row(f"{tag}: mlstm (gates, recurrence)",
+            lambda: ops.mlstm(proj, pre, bias_i, bias_f, 15.0, cache.state_view(0, 0), cache.state_view(0, 1), rows_, Hm, dk, dv,
+                              dk ** -0.5),
+            nbytes=state_bytes + tokens * (Hm * (2 * dk + dv) * 2 + Hm * dv * 4), flops=6.0 * tokens * Hm * dk * dv,
+            flop_peak=FP32_CORE_TFLOPS * 1e12, like=f"{tag}: delta_rule (conv, norms, recurrence)")
+        if len(tag) >= 8:
+            continue
+        o = rnd(tokens, Hm, dv)
+        w_all, w_one = 1 + rnd(Hm * dv) * 0.1, 1 + rnd(dv) * 0.1
+        row(f"{tag}: gated_head_norm (silu, one gain)",
+            lambda: ops.gated_head_norm(o, dproj, shape.gate_offset, w_one, 1e-6, Hm, dv, bf), nbytes=tokens * Hm * dv * 8)
+        row(f"{tag}: gated_head_norm (logistic, a gain over all heads)",
+            lambda: ops.gated_head_norm(o, proj, Hm * (2 * dk + dv), w_all, 1e-6, Hm, dv, bf, gate_kind="logistic"),
+            nbytes=tokens * Hm * dv * 8, like=f"{tag}: gated_head_norm (silu, one gain)")
+    ops.raise_on_device_error(err, "kernel table")
+    for name, r in rows.items():
+        if r["like"] in rows:
+            r["times_farther_than_like"] = round(rows[r["like"]]["frac"] / r["frac"], 2)
+    return rows
+
+
 def run_design(args):
     import torch
     from thing_htn_2026_b200 import Engine, ops
@@ -663,31 +890,35 @@ def run_design(args):
     sampler = ClockSampler()
     sampler.start()
     ops.launch_count = 0
-    for name in DESIGN_SIZES:
+    design = args.design
+    design_sizes = DESIGN_SIZES if design == "lanilix" else BUNUDRA_SIZES
+    for name in design_sizes:
         lan = named_config_json(name)
         if args.layers:
             lan["layers"] = lan["layers"][:args.layers]
         per_seq = -(-(args.prompt_len + warmup + steps + 2) // 64) * 64
         max_tokens = max(args.batch * per_seq, PREFILL_TOKENS + 64) + 64
         entry = {"layers": [l["type"] for l in lan["layers"]], "width": lan["width"]}
-        for label, data in (("lanilix", lan), ("qwen3_same_size", qwen3_like(lan))):
+        beside = ("qwen3_same_size", qwen3_like(lan)) if design == "lanilix" else ("lanilix_same_size", lanilix_like(lan))
+        for label, data in ((design, lan), beside):
             engine = Engine.from_config(config_from_dict(data), seed=0, dtype="bfloat16", max_tokens=max_tokens,
                                         max_batch=args.batch)
             entry[label] = measure_model(torch, engine, data.get("vocab", data.get("vocab_size")), args.batch,
                                          args.prompt_len, steps, warmup)
             del engine
             torch.cuda.empty_cache()
-        entry["kernels"] = kernel_table(torch, lan, peak, args.batch, args.prompt_len)
+        table = kernel_table if design == "lanilix" else bunudra_kernel_table
+        entry["kernels"] = table(torch, lan, peak, args.batch, args.prompt_len)
         sizes[name] = entry
     clocks = sampler.stop()
-    first = sizes[DESIGN_SIZES[0]]
+    first = sizes[design_sizes[0]]
     print(json.dumps({
-        "metric": f"decode tok/s at batch {args.batch} (Lanilix, {DESIGN_SIZES[0]}, random bf16 weights, 1 B200)",
-        "value": first["lanilix"]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
-        "ms_per_step": first["lanilix"]["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "metric": f"decode tok/s at batch {args.batch} ({design.capitalize()}, {design_sizes[0]}, random bf16 weights, 1 B200)",
+        "value": first[design]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": first[design]["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random-init weights, seeded uniform-random token ids",
-        "impl": "ours", "design": "lanilix",
-        "config": {"model": DESIGN_SIZES[0], "global_batch": args.batch, "seq_len": args.prompt_len + warmup + steps,
+        "impl": "ours", "design": design,
+        "config": {"model": design_sizes[0], "global_batch": args.batch, "seq_len": args.prompt_len + warmup + steps,
                    "prompt_len": args.prompt_len, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
                    "l2": "kernel table: a 256 MB buffer is written between timed launches", "peaks": peak["source"],
                    "fp32_core_tflops": FP32_CORE_TFLOPS},
@@ -891,9 +1122,9 @@ def main():
                              "(for ncu --profile-from-start off)")
     parser.add_argument("--workload", choices=sorted(LARGE_WORKLOADS), default=None,
                         help="one of the two larger workloads instead of the default run")
-    parser.add_argument("--design", choices=["lanilix"], default=None,
-                        help="another design beside a Qwen3 decoder of the same sizes, model by model and kernel by "
-                             "kernel, instead of the default run")
+    parser.add_argument("--design", choices=["lanilix", "bunudra"], default=None,
+                        help="another design beside its closest relative at the same sizes (Lanilix beside Qwen3, "
+                             "Bunudra beside Lanilix), model by model and kernel by kernel, instead of the default run")
     args = parser.parse_args()
     args.steps_given = args.steps is not None
     if args.steps is None:

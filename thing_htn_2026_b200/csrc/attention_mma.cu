@@ -17,12 +17,20 @@
 #include "common.cuh"
 
 // The keys a query may see besides causality: the last `size` positions (0: all), and with a
-// window also the first `keep` positions of the sequence.  Reads as the window's size where
-// only that is asked for.
+// window also the first `keep` positions of the sequence; or, with `chunk` > 0, the positions of
+// the query's own chunk of that many positions only (chunks counted from the sequence's first
+// position; no kept positions then).  Reads as the window's size where only that is asked for.
 struct KeyWindow {
-    int size, keep;
-    __host__ __device__ KeyWindow(int s = 0, int k = 0) : size(s), keep(s > 0 ? k : 0) {}
+    int size, keep, chunk;
+    __host__ __device__ KeyWindow(int s = 0, int k = 0, int c = 0) : size(s), keep(s > 0 ? k : 0), chunk(c) {}
     __host__ __device__ operator int() const { return size; }
+    // first position that the query at `pos` sees, kept first positions aside
+    __host__ __device__ int first_visible(int pos) const {
+        int first = 0;
+        if (size > 0 && pos - size + 1 > 0) first = pos - size + 1;
+        if (chunk > 0 && pos / chunk * chunk > first) first = pos / chunk * chunk;
+        return first;
+    }
 };
 
 namespace {
@@ -199,8 +207,7 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
     }
     cp_async_commit();
 
-    int first_key = 0;
-    if (window > 0 && pos0 - window + 1 > 0) first_key = pos0 - window + 1;
+    const int first_key = window.first_visible(pos0);
     const int t_first = first_key / kTile, t_last = pos_last / kTile;
     // Key tiles in the order they are visited: those of the kept first positions that lie before
     // the window's first tile, then the window's.
@@ -237,6 +244,8 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
     st.init();
     const int g = lane >> 2, tq = lane & 3;
     const int my_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};
+    const int my_chunk_start[2] = {window.chunk > 0 ? my_pos[0] / window.chunk * window.chunk : 0,
+                                   window.chunk > 0 ? my_pos[1] / window.chunk * window.chunk : 0};
 
     for (int visit = 0; visit < n_visits; ++visit) {
         const int t = tile_of(visit);
@@ -250,7 +259,8 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
         if (warp_active) {
             float s[8][4];
             qk_tile<D, 8>(s, qf, k_smem + stage * kTile * kPitch, 0, lane);
-            const bool need_mask = key0 + kTile - 1 > pos0 + warp * 16 || (window > 0 && key0 < pos0 + warp * 16 + 15 - window + 1);
+            const bool need_mask = key0 + kTile - 1 > pos0 + warp * 16 || (window > 0 && key0 < pos0 + warp * 16 + 15 - window + 1) ||
+                                   (window.chunk > 0 && key0 < window.first_visible(pos0 + warp * 16 + 15));
 #pragma unroll
             for (int n = 0; n < 8; ++n)
 #pragma unroll
@@ -259,7 +269,8 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
                     if (need_mask) {
                         const int key = key0 + n * 8 + tq * 2 + (i & 1);
                         const int p = my_pos[i >> 1];
-                        if (key > p || (window > 0 && key <= p - window && key >= window.keep)) v = -INFINITY;
+                        if (key > p || (window > 0 && key <= p - window && key >= window.keep) || key < my_chunk_start[i >> 1])
+                            v = -INFINITY;
                     }
                     s[n][i] = v;
                 }
@@ -426,8 +437,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     const int pos = row_pos[b];
     const int* pages = kv.block_table + (size_t)row_slot[b] * kv.bt_stride;
 
-    int first_key = 0;
-    if (window > 0 && pos - window + 1 > 0) first_key = pos - window + 1;
+    const int first_key = window.first_visible(pos);
     const int t_first = first_key / kTile, t_last = pos / kTile;
     // Key tiles are counted in the order they are visited: those of the kept first positions that
     // lie before the window's first tile, then the window's.  t_begin, t_end and the loop below
@@ -1524,7 +1534,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     // pairs of 1,024 keys on: 4.38 against 4.76 ms per step at batch 24 with 4,096 keys).
     const bool second_pass = (long long)n_pairs > (long long)sm_count() * decode_blocks_per_sm<D, 2>();
     const bool asked_for = (hints & 2) != 0;
-    if (n_splits == 1 && n_pages > 0 && window.keep == 0 && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
+    if (n_splits == 1 && n_pages > 0 && window.keep == 0 && window.chunk == 0 && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
         const int taken = g_decode_stream_stages >= 6
             ? launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
                                                 stream, fused, hints)
@@ -1605,14 +1615,16 @@ THN_API int thn_attention_prefill_tile_rows() { return kPrefillRows; }
 // Rows of a step that brings one or more tokens per sequence.  tile_row0[i] is the first
 // packed row of tile i, tile_rows[i] (1..thn_attention_prefill_tile_rows()) the number of its rows; the rows of a tile are
 // consecutive tokens of one sequence.  q, out [rows, n_q * head_dim] bfloat16.  With a window
-// (window_size > 0) the first keep_first positions of a sequence stay visible as well.
+// (window_size > 0) the first keep_first positions of a sequence stay visible as well; with
+// chunk > 0 (and no window) a row sees the keys of its own chunk of that many positions only.
 THN_API int thn_attention_prefill_bf16(void* out, const void* q, const int* tile_row0, const int* tile_rows,
                                        int n_tiles, const int* row_slot, const int* row_pos, const void* kv_base,
                                        const int* block_table, int bt_stride, int n_kv, int page_size, int head_dim,
-                                       int n_q, float scale, int window_size, int keep_first, int* err,
+                                       int n_q, float scale, int window_size, int keep_first, int chunk, int* err,
                                        cudaStream_t stream) {
-    THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && keep_first >= 0, "attention_prefill: bad sizes");
-    const KeyWindow window(window_size, keep_first);
+    THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && keep_first >= 0 && chunk >= 0, "attention_prefill: bad sizes");
+    THN_CHECK_ARG(chunk == 0 || (window_size <= 0 && keep_first == 0), "attention_prefill: chunks stand instead of a window");
+    const KeyWindow window(window_size, keep_first, chunk);
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
                        "attention_prefill: head_dim %d, page %d, heads %d/%d not supported by the tensor-core kernel",
                        head_dim, page_size, n_q, n_kv);
@@ -1691,11 +1703,12 @@ THN_API void thn_set_decode_stream(int mode, int stages) {
 THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_slot, const int* row_pos,
                                       const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                       int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
-                                      int window_size, int keep_first, float* scratch, int* counters, long long n_pages,
-                                      int hints, int* err, cudaStream_t stream) {
-    THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535 && keep_first >= 0,
+                                      int window_size, int keep_first, int chunk, float* scratch, int* counters,
+                                      long long n_pages, int hints, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535 && keep_first >= 0 && chunk >= 0,
                   "attention_decode: bad sizes");
-    const KeyWindow window(window_size, keep_first);
+    THN_CHECK_ARG(chunk == 0 || (window_size <= 0 && keep_first == 0), "attention_decode: chunks stand instead of a window");
+    const KeyWindow window(window_size, keep_first, chunk);
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode: at most 32 splits with counters, got %d",
                   n_splits);
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
@@ -1809,6 +1822,6 @@ THN_API int thn_attention_decode_bf16_no_alloc(void* out, const void* q, const i
         if (scratch == nullptr) return THN_BAD_ARGUMENT;
     }
     return thn_attention_decode_bf16(out, q, row_slot, row_pos, kv_base, block_table, bt_stride, n_kv, page_size,
-                                     head_dim, n_seqs, n_q, n_splits, scale, window, /*keep_first=*/0, scratch, nullptr, /*n_pages=*/0, /*hints=*/1, err,
+                                     head_dim, n_seqs, n_q, n_splits, scale, window, /*keep_first=*/0, /*chunk=*/0, scratch, nullptr, /*n_pages=*/0, /*hints=*/1, err,
                                      stream);
 }

@@ -94,10 +94,11 @@ _SIGNATURES = {
     "thn_attention_mma_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_fused_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
+                                   c_void_p],
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int,
-                                  c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_longlong,
+                                  c_int, c_void_p, c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
     "thn_attention_decode_cluster_splits": [],
     "thn_attention_decode_one_wave_splits": [c_int, c_int, c_int],
@@ -721,7 +722,7 @@ def prompt_attention_tile(dtype: torch.dtype, kv_head_dim: int, page_size: int, 
                           value_dim: Optional[int] = None, chunk: Optional[int] = None) -> int:
     """Rows per tile that the prompt attention kernel for these sizes works on, or 0 if the
     sizes go to the kernel that needs no tiles."""
-    if chunk or (value_dim is not None and value_dim != kv_head_dim):
+    if value_dim is not None and value_dim != kv_head_dim:
         return 0
     if dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv_head_dim, page_size, n_q, n_kv):
         return lib().thn_attention_prefill_tile_rows()
@@ -739,16 +740,17 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
     ``exact_weights`` asks for float32 softmax weights in the product with the values, which
     the kernels without tensor cores honour."""
     keep_first = int(keep_first or 0) if window else 0
-    if chunk or kv.v_dim != kv.head_dim:
+    if kv.v_dim != kv.head_dim:
         return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights)
     if q.dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
         if rows.max_q_len == 1:
-            return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first)
+            return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first, chunk=chunk)
         if tiles is not None:
-            if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
+            if not chunk and USE_TCGEN05_ATTENTION \
+                    and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
                 return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first)
-            return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first)
-    return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, exact_weights=exact_weights)
+            return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk)
+    return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights)
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
@@ -781,7 +783,8 @@ def _check_tiles(tiles: RowTiles) -> None:
 
 
 def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
-                           window: Optional[int], err: torch.Tensor, keep_first: int = 0) -> torch.Tensor:
+                           window: Optional[int], err: torch.Tensor, keep_first: int = 0,
+                           chunk: Optional[int] = None) -> torch.Tensor:
     """Tensor-core flash attention for steps with several tokens per sequence."""
     _need(q, "attention q", torch.bfloat16)
     out = torch.empty_like(q)
@@ -789,7 +792,7 @@ def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv:
     _call("thn_attention_prefill_bf16", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
           tiles.n, _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
           kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale), int(window or 0),
-          int(keep_first or 0), _ptr(err), _stream())
+          int(keep_first or 0), int(chunk or 0), _ptr(err), _stream())
     return out
 
 
@@ -852,7 +855,7 @@ def decode_hints(rows: StepRows, n_kv: int, n_splits: int, device) -> int:
 def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
                           window: Optional[int], err: torch.Tensor, n_splits: Optional[int] = None,
                           scratch: Optional[torch.Tensor] = None, fused_merge: bool = True,
-                          keep_first: int = 0) -> torch.Tensor:
+                          keep_first: int = 0, chunk: Optional[int] = None) -> torch.Tensor:
     """Split-KV flash decoding: one token per sequence.  Partial results of the splits go
     through float32 scratch memory, which is allocated here unless given."""
     _need(q, "attention q", torch.bfloat16)
@@ -869,7 +872,8 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     out = torch.empty_like(q)
     _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
-          n_seqs, n_q, n_splits, float(scale), int(window or 0), int(keep_first or 0), _ptr(scratch), _ptr(counters),
+          n_seqs, n_q, n_splits, float(scale), int(window or 0), int(keep_first or 0), int(chunk or 0), _ptr(scratch),
+          _ptr(counters),
           kv.storage.shape[0], decode_hints(rows, kv.n_kv, n_splits, q.device), _ptr(err), _stream())
     return out
 

@@ -24,7 +24,7 @@ csrc/latent_prepare.cu.
 
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Dict, List, Optional
 
 import torch
 
@@ -33,7 +33,7 @@ from ..cache.sequence_cache import CacheNeed, KVSpec
 from ..config.base import PartSpec, ScheduleEntry
 from ..weights.loader import GAIN, MATRIX, TensorSpec
 from .registry import part_class, register_part
-from .runtime import Runtime, StepContext
+from .runtime import HostBatch, Runtime, StepContext
 
 
 @register_part("mixer", "latent_attention")
@@ -91,14 +91,32 @@ class LatentAttention:
     def cache_need(self) -> CacheNeed:
         return KVSpec(self.n_heads, self.plain + self.rot, self.window, 0, None, self.value_dim)
 
+    def _tile(self, page_size: int) -> int:
+        return ops.prompt_attention_tile(self.dtype, self.plain + self.rot, page_size, self.n_heads, self.n_heads,
+                                         self.value_dim)
+
+    def step_inputs(self, batch: HostBatch, out: Dict[str, List[int]]) -> None:
+        """Row tiles for the tensor-core prompt kernel, where keys and values have one size that it
+        takes (the list is shared with every other attention that wants tiles of this size)."""
+        size = self._tile(batch.page_size) if batch.max_count > 1 else 0
+        if size and f"row_tiles/{size}/row0" not in out:
+            out[f"row_tiles/{size}/row0"], out[f"row_tiles/{size}/rows"] = ops.row_tiles_of(
+                batch.counts, batch.held, size)
+
     def forward(self, x: torch.Tensor, ctx: StepContext, entry: ScheduleEntry) -> torch.Tensor:
         kv = ctx.cache.kv_view(entry.cache)
+        tiles = None
+        if ctx.rows.max_q_len > 1:
+            size = self._tile(kv.page_size)
+            row0 = ctx.inputs.get(f"row_tiles/{size}/row0") if size else None
+            if row0 is not None:
+                tiles = ops.RowTiles(row0, ctx.inputs[f"row_tiles/{size}/rows"], row0.shape[0], size)
         proj = ops.linear(x, self.w_in, err=ctx.err)
         latent = ops.latent_norm(proj, self.latent_offset, self.rank, self.latent_gain, self.eps)
         up = ops.linear(latent, self.w_up, err=ctx.err)
         q = ops.latent_assemble(proj, 0, self.shared_offset, up, self.position.tables() if self.position else None,
                                 ctx.rows, kv, self.n_heads, self.plain, self.rot, ctx.err)
-        a = ops.attention(q, ctx.rows, kv, self.n_heads, self.scale, self.window, ctx.err,
+        a = ops.attention(q, ctx.rows, kv, self.n_heads, self.scale, self.window, ctx.err, tiles,
                           exact_weights=self.exact_weights)
         if self.gated:
             a = ops.logistic_gate(a, proj, self.gate_offset)
