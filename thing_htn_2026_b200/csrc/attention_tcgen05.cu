@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
     __nv_bfloat16* __restrict__ out, const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, const int* __restrict__ block_table,
-    int bt_stride, int n_kv, int n_q, float scale_log2, int window, int keep_first, int* __restrict__ err) {
+    int bt_stride, int n_kv, int n_q, float scale_log2, int window, int keep_first, int chunk, int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];      // swizzled tiles want 1024-byte alignment
@@ -235,6 +235,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     const int pos0 = row_pos[row0], pos_last = pos0 + n_rows - 1;
     int first_key = 0;
     if (window > 0 && pos0 - window + 1 > 0) first_key = pos0 - window + 1;
+    if (chunk > 0) first_key = max(first_key, pos0 / chunk * chunk);      // the first row's chunk starts first
     const int t_first = first_key / kKeys, t_last = pos_last / kKeys;
     // Key tiles in the order they are visited: those of the kept first positions that lie before
     // the window's first tile, then the window's.  Every role below counts visits.
@@ -384,12 +385,14 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
             float tile_max = -INFINITY;
             // a tile that every row of this warp sees whole needs no mask
             const int warp_first = pos0 + quarter * 32, warp_last = warp_first + 31;
-            const bool whole = key0 + kKeys - 1 <= warp_first && (window <= 0 || key0 > warp_last - window);
+            const bool whole = key0 + kKeys - 1 <= warp_first && (window <= 0 || key0 > warp_last - window) &&
+                               (chunk <= 0 || key0 >= warp_last / chunk * chunk);
+            const int chunk_start = chunk > 0 ? pos / chunk * chunk : 0;
             if (!whole) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     const int key = key0 + i;
-                    const bool visible = key <= pos && (window <= 0 || key > pos - window || key < keep_first);
+                    const bool visible = key <= pos && key >= chunk_start && (window <= 0 || key > pos - window || key < keep_first);
                     s[i] = visible ? s[i] : -INFINITY;
                 }
             }
@@ -541,14 +544,16 @@ THN_API int thn_attention_tcgen05_supported(int head_dim, int page_size, int n_q
 
 // Same contract as thn_attention_prefill_bf16 with row tiles of 128 rows (tile_rows 1..128);
 // n_rows_total is the number of packed rows of q and out, n_pages the pages of the cache entry.
-// With a window the first keep_first positions of a sequence stay visible as well.
+// With a window the first keep_first positions of a sequence stay visible as well; with chunk > 0
+// (and no window) a row sees the keys of its own chunk of that many positions only.
 THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* tile_row0, const int* tile_rows,
                                           int n_tiles, int n_rows_total, const int* row_slot, const int* row_pos,
                                           const void* kv_base, long long n_pages, const int* block_table,
                                           int bt_stride, int n_kv, int page_size, int head_dim, int n_q, float scale,
-                                          int window, int keep_first, int* err, cudaStream_t stream) {
-    THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && n_rows_total >= 0 && n_pages > 0 && keep_first >= 0,
+                                          int window, int keep_first, int chunk, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && n_rows_total >= 0 && n_pages > 0 && keep_first >= 0 && chunk >= 0,
                   "attention_tcgen05: bad sizes");
+    THN_CHECK_ARG(chunk == 0 || window <= 0, "attention_tcgen05: chunks stand instead of a window");
     THN_UNSUPPORTED_IF(!thn_attention_tcgen05_supported(head_dim, page_size, n_q, n_kv),
                        "attention_tcgen05: head_dim %d, page %d, heads %d/%d not supported", head_dim, page_size, n_q,
                        n_kv);
@@ -576,6 +581,6 @@ THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* t
     dim3 grid(n_q, n_tiles);
     thn_launch(attention_tcgen05_kernel, grid, kThreads, kSmemBytes, stream, map_q, map_kv, (__nv_bfloat16*)out,
                tile_row0, tile_rows, row_slot, row_pos, block_table, bt_stride, n_kv, n_q, scale * kLog2e, window,
-               window > 0 ? keep_first : 0, err);
+               window > 0 ? keep_first : 0, chunk, err);
     return thn_launch_status("attention_tcgen05");
 }

@@ -109,11 +109,39 @@ __global__ void logistic_gate_kernel(T* __restrict__ out, const T* __restrict__ 
     out[e] = from_f32<T>(to_f32<T>(a[e]) / (1.0f + expf(-z)));
 }
 
+// The same, eight bfloat16 entries per thread (16-byte accesses), one row per blockIdx.y.
+__global__ void logistic_gate_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ a,
+                                              const __nv_bfloat16* __restrict__ g, long long g_stride, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= width) return;
+    const long long row = blockIdx.y;
+    const uint4 ra = *reinterpret_cast<const uint4*>(a + row * width + c);
+    const uint4 rg = *reinterpret_cast<const uint4*>(g + row * g_stride + c);
+    const uint32_t ia[4] = {ra.x, ra.y, ra.z, ra.w}, ig[4] = {rg.x, rg.y, rg.z, rg.w};
+    uint32_t res[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ia[i]));
+        const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ig[i]));
+        const __nv_bfloat162 r = __floats2bfloat162_rn(x.x / (1.0f + expf(-z.x)), x.y / (1.0f + expf(-z.y)));
+        res[i] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    *reinterpret_cast<uint4*>(out + row * width + c) = make_uint4(res[0], res[1], res[2], res[3]);
+}
+
 THN_API int thn_logistic_gate(void* out, const void* a, const void* g, long long g_stride, int n_rows, int width,
                               int dtype, cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && width > 0 && g_stride >= width, "logistic_gate: bad sizes");
     const long long n = (long long)n_rows * width;
     if (n == 0) return THN_OK;
+    if (dtype == THN_BF16 && width % 8 == 0 && g_stride % 8 == 0 && n_rows <= 65535 &&
+        ((((uintptr_t)out) | ((uintptr_t)a) | ((uintptr_t)g)) & 15) == 0) {
+        thn_launch(logistic_gate_bf16_vec_kernel, dim3((width / 8 + 127) / 128, n_rows), 128, 0, stream, (__nv_bfloat16*)out,
+                   (const __nv_bfloat16*)a, (const __nv_bfloat16*)g, g_stride, width);
+        return thn_launch_status("logistic_gate");
+    }
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == THN_F32)
         thn_launch(logistic_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)a, (const float*)g,

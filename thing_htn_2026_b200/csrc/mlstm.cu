@@ -19,10 +19,15 @@
 //
 //   mlstm_gates        x, y -> i, f for every row and head of a step (rows are independent)
 //   mlstm_recurrence   the recurrence; with raw_gates it transforms x, y itself (single-token
-//                      steps: one kernel)
+//                      steps: one kernel); steps of several tokens take the kernel that stages
+//                      the tokens in shared memory where the rows' alignment allows it
 #include <math.h>
 
+#include <algorithm>
+
 #include "common.cuh"
+
+static int g_mlstm_staged = 1;       // 0: steps of several tokens run the kernel without staging too (measurement)
 
 namespace {
 
@@ -117,6 +122,141 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_kernel(
     if (threadIdx.x == 0) nm_block[D] = m;
 }
 
+// The same recurrence for steps of several tokens per sequence, with the tokens' operands staged
+// in shared memory: up to kStage tokens at a time (fewer for large keys), the next stage's q, k, v
+// and gates copied by cp.async while this stage is worked on.  The running maxima of a stage are
+// a short serial chain of additions and comparisons, which every thread walks; the three
+// exponentials of a token are then computed by one thread each.  Inside a stage a token costs a
+// column's lanes their multiply-adds, three shuffles per sum and one division.  The arithmetic,
+// and its order, are those of the kernel above.  Needs rows whose q, k and v parts start on
+// 16-byte boundaries (the launcher checks).
+constexpr int kStage = 16;
+
+__device__ __forceinline__ void copy16_async(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void copy4_async(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void copy_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+template <typename T, int R>
+__global__ void __launch_bounds__(kThreads) mlstm_recurrence_staged_kernel(
+    float* __restrict__ o, float* __restrict__ S, float* __restrict__ nm, const T* __restrict__ proj, int proj_width,
+    const float* __restrict__ gates, const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int n_heads, int D,
+    int E, float q_scale, float floor_, int stage_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char staged_raw[];
+    constexpr int kPer16 = 16 / (int)sizeof(T);                  // elements per 16-byte copy
+    const int row_elems = 2 * D + kColumns;                      // q, k, the block's 16 columns of v
+    T* buffers = reinterpret_cast<T*>(staged_raw);               // [2][stage_tokens][row_elems]
+    float* gate_i = reinterpret_cast<float*>(buffers + (size_t)2 * stage_tokens * row_elems);   // [2][kStage]
+    float* gate_f = gate_i + 2 * kStage;                         // [2][kStage]
+    float* keep_s = gate_f + 2 * kStage;                         // [kStage] exp(f + m - m')
+    float* take_s = keep_s + kStage;                             // [kStage] exp(i - m')
+    float* low_s = take_s + kStage;                              // [kStage] exp(-m')
+    const int seq = blockIdx.x, head = blockIdx.y, block_of_columns = blockIdx.z;
+    const int group = threadIdx.x / kLanes, lane = threadIdx.x % kLanes;
+    const int column = block_of_columns * kColumns + group;
+    const bool active = column < E;
+    const int slot = slots[seq];
+    const int row0 = cu_seqlens[seq], row1 = cu_seqlens[seq + 1];
+
+    float* s_col = S + (((size_t)slot * n_heads + head) * E + (active ? column : 0)) * D;
+    float* nm_block = nm + (((size_t)slot * n_heads + head) * gridDim.z + block_of_columns) * (D + 1);
+    float s[R], n[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int d = lane + kLanes * r;
+        s[r] = active && d < D ? s_col[d] : 0.f;
+        n[r] = d < D ? nm_block[d] : 0.f;
+    }
+    float m = nm_block[D];
+
+    const int copies_per_row = row_elems / kPer16;
+    auto issue = [&](int first_row, int buffer) {
+        const int count = min(stage_tokens, row1 - first_row);
+        T* dst = buffers + (size_t)buffer * stage_tokens * row_elems;
+        for (int c = threadIdx.x; c < count * copies_per_row; c += kThreads) {
+            const int t = c / copies_per_row, e = (c - t * copies_per_row) * kPer16;
+            const T* src = proj + (size_t)(first_row + t) * proj_width;
+            const T* from = e < D ? src + (size_t)head * D + e
+                          : e < 2 * D ? src + (size_t)(n_heads + head) * D + (e - D)
+                                      : src + (size_t)2 * n_heads * D + (size_t)head * E + block_of_columns * kColumns + (e - 2 * D);
+            copy16_async(dst + (size_t)t * row_elems + e, from);
+        }
+        if (threadIdx.x < count) {
+            const float* g = gates + (size_t)(first_row + threadIdx.x) * 2 * n_heads;
+            copy4_async(gate_i + buffer * kStage + threadIdx.x, g + head);
+            copy4_async(gate_f + buffer * kStage + threadIdx.x, g + n_heads + head);
+        }
+        copy_commit();
+    };
+
+    if (row0 < row1) issue(row0, 0);
+    int buffer = 0;
+    for (int first_row = row0; first_row < row1; first_row += stage_tokens, buffer ^= 1) {
+        const int count = min(stage_tokens, row1 - first_row);
+        copy_wait_all();
+        __syncthreads();                          // this stage has landed; the other buffer is free again
+        if (first_row + stage_tokens < row1) issue(first_row + stage_tokens, buffer ^ 1);
+        const float* gi = gate_i + buffer * kStage;
+        const float* gf = gate_f + buffer * kStage;
+        // the stage's running maxima: the same chain in every thread; a thread keeps the one before its own token
+        float running = m, before_mine = m;
+        for (int t = 0; t < count; ++t) {
+            if (t == (int)threadIdx.x) before_mine = running;
+            running = fmaxf(gf[t] + running, gi[t]);
+        }
+        if ((int)threadIdx.x < count) {
+            const int t = threadIdx.x;
+            const float m_new = fmaxf(gf[t] + before_mine, gi[t]);
+            keep_s[t] = expf(gf[t] + before_mine - m_new);
+            take_s[t] = expf(gi[t] - m_new);
+            low_s[t] = expf(-m_new);
+        }
+        m = running;
+        __syncthreads();
+        const T* stage = buffers + (size_t)buffer * stage_tokens * row_elems;
+        for (int t = 0; t < count; ++t) {
+            const T* q_src = stage + (size_t)t * row_elems;
+            const T* k_src = q_src + D;
+            const float v = active ? to_f32<T>(q_src[2 * D + group]) : 0.f;
+            const float keep = keep_s[t], take = take_s[t];
+            float top = 0.f, bottom = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int d = lane + kLanes * r;
+                const float k = d < D ? to_f32<T>(k_src[d]) : 0.f;
+                const float q = d < D ? to_f32<T>(q_src[d]) * q_scale : 0.f;
+                const float tk = take * k;
+                s[r] = keep * s[r] + tk * v;
+                n[r] = keep * n[r] + tk;
+                top += s[r] * q;
+                bottom += n[r] * q;
+            }
+#pragma unroll
+            for (int w = kLanes / 2; w > 0; w >>= 1) {
+                top += __shfl_xor_sync(0xffffffffu, top, w);
+                bottom += __shfl_xor_sync(0xffffffffu, bottom, w);
+            }
+            if (active && lane == 0)
+                o[((size_t)(first_row + t) * n_heads + head) * E + column] = top / (fmaxf(fabsf(bottom), low_s[t]) + floor_);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int d = lane + kLanes * r;
+        if (d < D) {
+            if (active) s_col[d] = s[r];
+            if (group == 0) nm_block[d] = n[r];
+        }
+    }
+    if (threadIdx.x == 0) nm_block[D] = m;
+}
+
 template <typename T>
 int launch_recurrence(float* o, float* S, float* nm, const void* proj, int proj_width, const float* gates,
                       const float* bias_i, const float* bias_f, float cap, int raw_gates, const int* cu_seqlens,
@@ -124,6 +264,28 @@ int launch_recurrence(float* o, float* S, float* nm, const void* proj, int proj_
                       cudaStream_t stream) {
     const dim3 grid(n_seqs, n_heads, (E + kColumns - 1) / kColumns);
     const int per_lane = (D + kLanes - 1) / kLanes;
+    // Steps of several tokens go through shared memory where every 16-byte copy is aligned and stays
+    // inside its row: q, k and v parts of whole 16-byte pieces, and room behind a head's last columns.
+    const int unit = 16 / (int)sizeof(T);
+    const bool staged = !raw_gates && g_mlstm_staged && D % unit == 0 && E % unit == 0 && proj_width % unit == 0 &&
+                        ((uintptr_t)proj & 15) == 0 && ((uintptr_t)gates & 3) == 0 &&
+                        (E % kColumns == 0 || n_heads * (2 * D + E) + kColumns <= proj_width);
+    if (staged) {
+        const int row_bytes = (2 * D + kColumns) * (int)sizeof(T);
+        const int stage_tokens = std::max(1, std::min(kStage, 32768 / (2 * row_bytes)));
+        const size_t smem = (size_t)2 * stage_tokens * row_bytes + 7 * kStage * sizeof(float);
+#define THN_MLSTM_STAGED(R)                                                                                            \
+    thn_launch_ordered(mlstm_recurrence_staged_kernel<T, R>, grid, kThreads, smem, stream, o, S, nm, (const T*)proj,    \
+                       proj_width, gates, cu_seqlens, slots, n_heads, D, E, q_scale, floor_, stage_tokens)
+        if (per_lane <= 2) THN_MLSTM_STAGED(2);
+        else if (per_lane <= 4) THN_MLSTM_STAGED(4);
+        else if (per_lane <= 8) THN_MLSTM_STAGED(8);
+        else if (per_lane <= 16) THN_MLSTM_STAGED(16);
+        else if (per_lane <= 32) THN_MLSTM_STAGED(32);
+        else THN_MLSTM_STAGED(64);
+#undef THN_MLSTM_STAGED
+        return thn_launch_status("mlstm_recurrence");
+    }
 #define THN_MLSTM_LAUNCH(R)                                                                                          \
     thn_launch_ordered(mlstm_recurrence_kernel<T, R>, grid, kThreads, 0, stream, o, S, nm, (const T*)proj, proj_width, \
                        gates, bias_i, bias_f, cap, raw_gates, cu_seqlens, slots, n_heads, D, E, q_scale, floor_)
@@ -140,6 +302,8 @@ int launch_recurrence(float* o, float* S, float* nm, const void* proj, int proj_
 }  // namespace
 
 THN_API int thn_mlstm_columns_per_block() { return kColumns; }
+
+THN_API void thn_set_mlstm_staged(int on) { g_mlstm_staged = on ? 1 : 0; }
 
 // pre [rows, 2 * heads] (x of every head, then y of every head), biases [heads]; out the same
 // shape: i, then f.

@@ -124,6 +124,36 @@ __global__ void routed_gelu_kernel(T* __restrict__ out, const T* __restrict__ u,
     out[e] = from_f32<T>(gelu_exact(to_f32<T>(u[e])) * w);
 }
 
+// The same, eight bfloat16 columns per thread (16-byte accesses), one row per blockIdx.y: for
+// sizes where no group of eight columns straddles two experts.  The columns of an expert that
+// was not chosen are not read.
+__global__ void routed_gelu_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ u,
+                                            const float* __restrict__ dense, const float* __restrict__ shared_logit,
+                                            long long logit_stride, int width, int n_experts, int ff) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= width) return;
+    const long long row = blockIdx.y;
+    float w;
+    if (c < n_experts * ff) w = dense[row * n_experts + c / ff];
+    else w = shared_logit ? 1.0f / (1.0f + expf(-shared_logit[row * logit_stride])) : 1.0f;
+    uint4 packed = make_uint4(0, 0, 0, 0);
+    if (w != 0.f) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(u + row * width + c);
+        const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t res[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in[i]));
+            const __nv_bfloat162 r = __floats2bfloat162_rn(gelu_exact(v.x) * w, gelu_exact(v.y) * w);
+            res[i] = *reinterpret_cast<const uint32_t*>(&r);
+        }
+        packed = make_uint4(res[0], res[1], res[2], res[3]);
+    }
+    *reinterpret_cast<uint4*>(out + row * width + c) = packed;
+}
+
 }  // namespace
 
 // z float32 [rows, >= experts] with rows z_stride apart; dense float32 [rows, experts]; chosen
@@ -154,6 +184,12 @@ THN_API int thn_routed_gelu(void* out, const void* u, const float* dense, const 
     const long long n = (long long)n_rows * width;
     if (n == 0) return THN_OK;
     const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == THN_BF16 && ff % 8 == 0 && width % 8 == 0 && n_rows <= 65535 &&
+        ((((uintptr_t)out) | ((uintptr_t)u)) & 15) == 0) {
+        thn_launch(routed_gelu_bf16_vec_kernel, dim3((width / 8 + 127) / 128, n_rows), 128, 0, stream, (__nv_bfloat16*)out,
+                   (const __nv_bfloat16*)u, dense, shared_logit, logit_stride, width, n_experts, ff);
+        return thn_launch_status("routed_gelu");
+    }
     if (dtype == THN_F32)
         thn_launch(routed_gelu_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)u, dense, shared_logit,
                    logit_stride, n, width, n_experts, ff);

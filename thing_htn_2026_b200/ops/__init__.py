@@ -109,7 +109,7 @@ _SIGNATURES = {
     "thn_attention_tcgen05_test_skip_loads": [c_int],
     "thn_attention_prefill_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                      c_int, c_int, c_void_p, c_void_p],
+                                      c_int, c_int, c_int, c_void_p, c_void_p],
 }
 
 _lib = None
@@ -140,6 +140,9 @@ def lib():
         loaded.thn_set_decode_stream.restype = None
         loaded.thn_set_decode_stream(int(os.environ.get("THN_DECODE_STREAM", 1)),
                                      int(os.environ.get("THN_DECODE_STREAM_STAGES", 3)))
+        loaded.thn_set_mlstm_staged.argtypes = [c_int]
+        loaded.thn_set_mlstm_staged.restype = None
+        loaded.thn_set_mlstm_staged(0 if os.environ.get("THN_MLSTM_STAGED", "1").strip() in ("0", "false", "off") else 1)
         loaded.thn_choose_tokens_scratch_floats.argtypes = [c_int, c_int]
         loaded.thn_choose_tokens_scratch_floats.restype = c_longlong
         loaded.thn_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
@@ -746,15 +749,15 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
         if rows.max_q_len == 1:
             return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first, chunk=chunk)
         if tiles is not None:
-            if not chunk and USE_TCGEN05_ATTENTION \
-                    and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
-                return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first)
+            if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
+                return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk)
             return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk)
     return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights)
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
-                              window: Optional[int], err: torch.Tensor, keep_first: int = 0) -> torch.Tensor:
+                              window: Optional[int], err: torch.Tensor, keep_first: int = 0,
+                              chunk: Optional[int] = None) -> torch.Tensor:
     """tcgen05 / TMEM / TMA flash attention for steps with several tokens per sequence
     (bfloat16, head size 128)."""
     _need(q, "attention q", torch.bfloat16)
@@ -763,7 +766,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, 
     _call("thn_attention_prefill_tcgen05", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
           tiles.n, q.shape[0], _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), kv.storage.shape[0],
           _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale),
-          int(window or 0), int(keep_first or 0), _ptr(err), _stream())
+          int(window or 0), int(keep_first or 0), int(chunk or 0), _ptr(err), _stream())
     return out
 
 
