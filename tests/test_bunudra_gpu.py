@@ -310,6 +310,33 @@ def test_mixer_alone_whole_in_portions_and_token_by_token(models, dtype, name, l
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("staged, lanes", [(False, 0), (True, 8), (True, 32)])
+@pytest.mark.parametrize("name, layer", [m for m in MIXERS if tiny.CONFIGS[m[0]]["layers"][m[1]]["type"] == "mlstm"])
+def test_matrix_memory_with_every_prompt_kernel(models, dtype, staged, lanes, name, layer):
+    """The recurrence over a prompt with the plain kernel, with tokens staged in shared memory at 8
+    and at 32 lanes per column (sizes whose rows are not aligned fall back to the plain kernel by
+    themselves): a prompt longer than several stages, cut so that a stage is left partly filled,
+    then continued token by token from the state the prompt left."""
+    from thing_htn_2026_b200 import ops
+    folder = models[name]
+    part, config = part_of(folder, layer, "mixer", dtype)
+    data = tiny.config_json(name)["layers"][layer]
+    _, w = read(folder)
+    x = rand((83, config.width), 400 + layer).to(TORCH[dtype])
+    precision = torch.float32 if dtype == "float32" else torch.bfloat16
+    want = plain_mixer(data, x.float(), w, f"l{layer}.mix.", config.norm_eps, precision)
+    ops.set_mlstm_kernel(staged, lanes)
+    try:
+        stepper = Stepper(part, dtype)
+        (a,) = stepper.cache.open(1)
+        got = [stepper.step([a], [x[:37]])[0], stepper.step([a], [x[37:70]])[0]]
+        got += [stepper.step([a], [x[i:i + 1]])[0] for i in range(70, 83)]
+    finally:
+        ops.set_mlstm_kernel()
+    close(torch.cat(got), want, dtype, f"staged={staged}, {lanes} lanes")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name, layer", [("a", 0), ("a", 3), ("b", 0), ("c", 1)])
 def test_feed_forward_alone(models, dtype, name, layer):
     """Routed experts with groups, a shared expert with its gate, one expert per token without a

@@ -28,6 +28,7 @@
 #include "common.cuh"
 
 static int g_mlstm_staged = 1;       // 0: steps of several tokens run the kernel without staging too (measurement)
+static int g_mlstm_lanes = 0;        // lanes per column in the staged kernel: 8, 32, or 0: by the step's size
 
 namespace {
 
@@ -129,7 +130,10 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_kernel(
 // exponentials of a token are then computed by one thread each.  Inside a stage a token costs a
 // column's lanes their multiply-adds, three shuffles per sum and one division.  The arithmetic,
 // and its order, are those of the kernel above.  Needs rows whose q, k and v parts start on
-// 16-byte boundaries (the launcher checks).
+// 16-byte boundaries (the launcher checks).  LANES lanes hold a column: 8, or 32 where a step has
+// no more (sequence, head, 16 columns) blocks than the GPU has SMs, so that 8 lanes would leave
+// every scheduler a single warp (0.92 against 1.00 ms for one prompt of 2,048 tokens with 16 heads
+// of 128 x 128; with 32 heads 8 lanes are ahead, 1.17 against 1.55 ms).
 constexpr int kStage = 16;
 
 __device__ __forceinline__ void copy16_async(void* smem, const void* gmem) {
@@ -141,8 +145,8 @@ __device__ __forceinline__ void copy4_async(void* smem, const void* gmem) {
 __device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 __device__ __forceinline__ void copy_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 
-template <typename T, int R>
-__global__ void __launch_bounds__(kThreads) mlstm_recurrence_staged_kernel(
+template <typename T, int R, int LANES>
+__global__ void __launch_bounds__(LANES * kColumns) mlstm_recurrence_staged_kernel(
     float* __restrict__ o, float* __restrict__ S, float* __restrict__ nm, const T* __restrict__ proj, int proj_width,
     const float* __restrict__ gates, const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int n_heads, int D,
     int E, float q_scale, float floor_, int stage_tokens) {
@@ -158,7 +162,8 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_staged_kernel(
     float* take_s = keep_s + kStage;                             // [kStage] exp(i - m')
     float* low_s = take_s + kStage;                              // [kStage] exp(-m')
     const int seq = blockIdx.x, head = blockIdx.y, block_of_columns = blockIdx.z;
-    const int group = threadIdx.x / kLanes, lane = threadIdx.x % kLanes;
+    constexpr int kBlock = LANES * kColumns;
+    const int group = threadIdx.x / LANES, lane = threadIdx.x % LANES;
     const int column = block_of_columns * kColumns + group;
     const bool active = column < E;
     const int slot = slots[seq];
@@ -169,7 +174,7 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_staged_kernel(
     float s[R], n[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int d = lane + kLanes * r;
+        const int d = lane + LANES * r;
         s[r] = active && d < D ? s_col[d] : 0.f;
         n[r] = d < D ? nm_block[d] : 0.f;
     }
@@ -179,7 +184,7 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_staged_kernel(
     auto issue = [&](int first_row, int buffer) {
         const int count = min(stage_tokens, row1 - first_row);
         T* dst = buffers + (size_t)buffer * stage_tokens * row_elems;
-        for (int c = threadIdx.x; c < count * copies_per_row; c += kThreads) {
+        for (int c = threadIdx.x; c < count * copies_per_row; c += kBlock) {
             const int t = c / copies_per_row, e = (c - t * copies_per_row) * kPer16;
             const T* src = proj + (size_t)(first_row + t) * proj_width;
             const T* from = e < D ? src + (size_t)head * D + e
@@ -228,7 +233,7 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_staged_kernel(
             float top = 0.f, bottom = 0.f;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const int d = lane + kLanes * r;
+                const int d = lane + LANES * r;
                 const float k = d < D ? to_f32<T>(k_src[d]) : 0.f;
                 const float q = d < D ? to_f32<T>(q_src[d]) * q_scale : 0.f;
                 const float tk = take * k;
@@ -238,7 +243,7 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_staged_kernel(
                 bottom += n[r] * q;
             }
 #pragma unroll
-            for (int w = kLanes / 2; w > 0; w >>= 1) {
+            for (int w = LANES / 2; w > 0; w >>= 1) {
                 top += __shfl_xor_sync(0xffffffffu, top, w);
                 bottom += __shfl_xor_sync(0xffffffffu, bottom, w);
             }
@@ -248,7 +253,7 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_staged_kernel(
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int d = lane + kLanes * r;
+        const int d = lane + LANES * r;
         if (d < D) {
             if (active) s_col[d] = s[r];
             if (group == 0) nm_block[d] = n[r];
@@ -274,15 +279,26 @@ int launch_recurrence(float* o, float* S, float* nm, const void* proj, int proj_
         const int row_bytes = (2 * D + kColumns) * (int)sizeof(T);
         const int stage_tokens = std::max(1, std::min(kStage, 32768 / (2 * row_bytes)));
         const size_t smem = (size_t)2 * stage_tokens * row_bytes + 7 * kStage * sizeof(float);
-#define THN_MLSTM_STAGED(R)                                                                                            \
-    thn_launch_ordered(mlstm_recurrence_staged_kernel<T, R>, grid, kThreads, smem, stream, o, S, nm, (const T*)proj,    \
-                       proj_width, gates, cu_seqlens, slots, n_heads, D, E, q_scale, floor_, stage_tokens)
-        if (per_lane <= 2) THN_MLSTM_STAGED(2);
-        else if (per_lane <= 4) THN_MLSTM_STAGED(4);
-        else if (per_lane <= 8) THN_MLSTM_STAGED(8);
-        else if (per_lane <= 16) THN_MLSTM_STAGED(16);
-        else if (per_lane <= 32) THN_MLSTM_STAGED(32);
-        else THN_MLSTM_STAGED(64);
+#define THN_MLSTM_STAGED(R, LANES)                                                                                     \
+    thn_launch_ordered(mlstm_recurrence_staged_kernel<T, R, LANES>, grid, LANES * kColumns, smem, stream, o, S, nm,     \
+                       (const T*)proj, proj_width, gates, cu_seqlens, slots, n_heads, D, E, q_scale, floor_, stage_tokens)
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+        const long long blocks = (long long)grid.x * grid.y * grid.z;
+        const bool wide = g_mlstm_lanes == 32 || (g_mlstm_lanes == 0 && D >= 32 && blocks <= sms);
+        if (wide) {
+            const int per32 = (D + 31) / 32;
+            if (per32 <= 1) THN_MLSTM_STAGED(1, 32);
+            else if (per32 <= 2) THN_MLSTM_STAGED(2, 32);
+            else if (per32 <= 4) THN_MLSTM_STAGED(4, 32);
+            else if (per32 <= 8) THN_MLSTM_STAGED(8, 32);
+            else THN_MLSTM_STAGED(16, 32);
+        } else if (per_lane <= 2) THN_MLSTM_STAGED(2, 8);
+        else if (per_lane <= 4) THN_MLSTM_STAGED(4, 8);
+        else if (per_lane <= 8) THN_MLSTM_STAGED(8, 8);
+        else if (per_lane <= 16) THN_MLSTM_STAGED(16, 8);
+        else if (per_lane <= 32) THN_MLSTM_STAGED(32, 8);
+        else THN_MLSTM_STAGED(64, 8);
 #undef THN_MLSTM_STAGED
         return thn_launch_status("mlstm_recurrence");
     }
@@ -303,7 +319,10 @@ int launch_recurrence(float* o, float* S, float* nm, const void* proj, int proj_
 
 THN_API int thn_mlstm_columns_per_block() { return kColumns; }
 
-THN_API void thn_set_mlstm_staged(int on) { g_mlstm_staged = on ? 1 : 0; }
+THN_API void thn_set_mlstm_staged(int on, int lanes) {
+    g_mlstm_staged = on ? 1 : 0;
+    g_mlstm_lanes = lanes == 8 || lanes == 32 ? lanes : 0;
+}
 
 // pre [rows, 2 * heads] (x of every head, then y of every head), biases [heads]; out the same
 // shape: i, then f.

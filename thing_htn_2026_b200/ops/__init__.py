@@ -140,9 +140,10 @@ def lib():
         loaded.thn_set_decode_stream.restype = None
         loaded.thn_set_decode_stream(int(os.environ.get("THN_DECODE_STREAM", 1)),
                                      int(os.environ.get("THN_DECODE_STREAM_STAGES", 3)))
-        loaded.thn_set_mlstm_staged.argtypes = [c_int]
+        loaded.thn_set_mlstm_staged.argtypes = [c_int, c_int]
         loaded.thn_set_mlstm_staged.restype = None
-        loaded.thn_set_mlstm_staged(0 if os.environ.get("THN_MLSTM_STAGED", "1").strip() in ("0", "false", "off") else 1)
+        loaded.thn_set_mlstm_staged(0 if os.environ.get("THN_MLSTM_STAGED", "1").strip() in ("0", "false", "off") else 1,
+                                    int(os.environ.get("THN_MLSTM_LANES", 0)))
         loaded.thn_choose_tokens_scratch_floats.argtypes = [c_int, c_int]
         loaded.thn_choose_tokens_scratch_floats.restype = c_longlong
         loaded.thn_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
@@ -1065,6 +1066,12 @@ def mlstm_column_blocks(value_dim: int) -> int:
     return -(-int(value_dim) // MLSTM_COLUMNS_PER_BLOCK)
 
 
+def set_mlstm_kernel(staged: bool = True, lanes: int = 0) -> None:
+    """Which kernel steps of several tokens take (tests and measurement): the one that stages
+    tokens in shared memory or the plain one; 8 or 32 lanes per column, or 0: by the step's size."""
+    lib().thn_set_mlstm_staged(int(bool(staged)), int(lanes))
+
+
 def mlstm(proj: torch.Tensor, gate_pre: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,
           state: torch.Tensor, normaliser: torch.Tensor, rows: StepRows, n_heads: int, key_dim: int, value_dim: int,
           q_scale: float, floor: float = 1e-6) -> torch.Tensor:
@@ -1188,5 +1195,5 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 __all__ = [
     "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "RowTiles", "StepRows", "row_tiles_of", "prompt_attention_tile", "linear_stream", "linear_swiglu", "linear_tcgen05", "add_rmsnorm", "advance",
     "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "attention_prefill_tcgen05", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
-    "qk_norm_rope_cache", "qk_prepare", "Gain", "STREAM_AS_IS", "residual_norm", "gather_rows_scaled", "logistic_gate", "latent_norm", "latent_assemble", "mlstm", "mlstm_column_blocks", "Routing", "moe_route", "routed_gelu", "gated_head_norm", "clamped_glu", "DeltaShape", "delta_rule", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
+    "qk_norm_rope_cache", "qk_prepare", "Gain", "STREAM_AS_IS", "residual_norm", "gather_rows_scaled", "logistic_gate", "latent_norm", "latent_assemble", "mlstm", "mlstm_column_blocks", "set_mlstm_kernel", "Routing", "moe_route", "routed_gelu", "gated_head_norm", "clamped_glu", "DeltaShape", "delta_rule", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]
