@@ -36,6 +36,12 @@ constexpr int kLanes = 8;            // lanes per column of S
 constexpr int kColumns = 16;         // columns per block
 constexpr int kThreads = kLanes * kColumns;
 
+// What the state is carried in between a step's first and last token: float beside bfloat16
+// activations; double on the true 32-bit path, where the sums over a long prompt would otherwise
+// gather float32 roundings that a cancelling n . q magnifies (the state in memory is float32).
+template <typename T> struct Carry { using type = float; };
+template <> struct Carry<float> { using type = double; };
+
 __device__ __forceinline__ float log_input_gate(float x, float cap) { return cap * tanhf(x / cap); }
 __device__ __forceinline__ float log_forget_gate(float y, float cap) {
     const float z = cap * tanhf(y / cap);
@@ -69,12 +75,13 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_kernel(
 
     float* s_col = S + (((size_t)slot * n_heads + head) * E + (active ? column : 0)) * D;
     float* nm_block = nm + (((size_t)slot * n_heads + head) * gridDim.z + block_of_columns) * (D + 1);
-    float s[R], n[R];
+    using A = typename Carry<T>::type;
+    A s[R], n[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = lane + kLanes * r;
-        s[r] = active && d < D ? s_col[d] : 0.f;
-        n[r] = d < D ? nm_block[d] : 0.f;
+        s[r] = active && d < D ? (A)s_col[d] : (A)0;
+        n[r] = d < D ? (A)nm_block[d] : (A)0;
     }
     float m = nm_block[D];
     const float bi = raw_gates ? bias_i[head] : 0.f, bf = raw_gates ? bias_f[head] : 0.f;
@@ -91,15 +98,15 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_kernel(
         }
         const float m_new = fmaxf(gf + m, gi);
         const float keep = expf(gf + m - m_new), take = expf(gi - m_new);
-        float top = 0.f, bottom = 0.f;
+        A top = 0, bottom = 0;
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const int d = lane + kLanes * r;
             const float k = d < D ? to_f32<T>(k_src[d]) : 0.f;
             const float q = d < D ? to_f32<T>(q_src[d]) * q_scale : 0.f;
-            const float tk = take * k;
-            s[r] = keep * s[r] + tk * v;
-            n[r] = keep * n[r] + tk;
+            const A tk = (A)take * k;
+            s[r] = (A)keep * s[r] + tk * v;
+            n[r] = (A)keep * n[r] + tk;
             top += s[r] * q;
             bottom += n[r] * q;
         }
@@ -110,14 +117,14 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_kernel(
         }
         m = m_new;
         if (active && lane == 0)
-            o[((size_t)row * n_heads + head) * E + column] = top / (fmaxf(fabsf(bottom), expf(-m)) + floor_);
+            o[((size_t)row * n_heads + head) * E + column] = (float)(top / (fmax(fabs(bottom), (A)expf(-m)) + (A)floor_));
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = lane + kLanes * r;
         if (d < D) {
-            if (active) s_col[d] = s[r];
-            if (group == 0) nm_block[d] = n[r];
+            if (active) s_col[d] = (float)s[r];
+            if (group == 0) nm_block[d] = (float)n[r];
         }
     }
     if (threadIdx.x == 0) nm_block[D] = m;
@@ -171,12 +178,13 @@ __global__ void __launch_bounds__(LANES * kColumns) mlstm_recurrence_staged_kern
 
     float* s_col = S + (((size_t)slot * n_heads + head) * E + (active ? column : 0)) * D;
     float* nm_block = nm + (((size_t)slot * n_heads + head) * gridDim.z + block_of_columns) * (D + 1);
-    float s[R], n[R];
+    using A = typename Carry<T>::type;
+    A s[R], n[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = lane + LANES * r;
-        s[r] = active && d < D ? s_col[d] : 0.f;
-        n[r] = d < D ? nm_block[d] : 0.f;
+        s[r] = active && d < D ? (A)s_col[d] : (A)0;
+        n[r] = d < D ? (A)nm_block[d] : (A)0;
     }
     float m = nm_block[D];
 
@@ -230,15 +238,15 @@ __global__ void __launch_bounds__(LANES * kColumns) mlstm_recurrence_staged_kern
             const T* k_src = q_src + D;
             const float v = active ? to_f32<T>(q_src[2 * D + group]) : 0.f;
             const float keep = keep_s[t], take = take_s[t];
-            float top = 0.f, bottom = 0.f;
+            A top = 0, bottom = 0;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const int d = lane + LANES * r;
                 const float k = d < D ? to_f32<T>(k_src[d]) : 0.f;
                 const float q = d < D ? to_f32<T>(q_src[d]) * q_scale : 0.f;
-                const float tk = take * k;
-                s[r] = keep * s[r] + tk * v;
-                n[r] = keep * n[r] + tk;
+                const A tk = (A)take * k;
+                s[r] = (A)keep * s[r] + tk * v;
+                n[r] = (A)keep * n[r] + tk;
                 top += s[r] * q;
                 bottom += n[r] * q;
             }
@@ -248,15 +256,16 @@ __global__ void __launch_bounds__(LANES * kColumns) mlstm_recurrence_staged_kern
                 bottom += __shfl_xor_sync(0xffffffffu, bottom, w);
             }
             if (active && lane == 0)
-                o[((size_t)(first_row + t) * n_heads + head) * E + column] = top / (fmaxf(fabsf(bottom), low_s[t]) + floor_);
+                o[((size_t)(first_row + t) * n_heads + head) * E + column] =
+                    (float)(top / (fmax(fabs(bottom), (A)low_s[t]) + (A)floor_));
         }
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = lane + LANES * r;
         if (d < D) {
-            if (active) s_col[d] = s[r];
-            if (group == 0) nm_block[d] = n[r];
+            if (active) s_col[d] = (float)s[r];
+            if (group == 0) nm_block[d] = (float)n[r];
         }
     }
     if (threadIdx.x == 0) nm_block[D] = m;
