@@ -310,11 +310,11 @@ def test_mixer_alone_whole_in_portions_and_token_by_token(models, dtype, name, l
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("staged, lanes", [(False, 0), (True, 8), (True, 32)])
+@pytest.mark.parametrize("staged, lanes", [(False, 0), (True, 8), (True, 16), (True, 32)])
 @pytest.mark.parametrize("name, layer", [m for m in MIXERS if tiny.CONFIGS[m[0]]["layers"][m[1]]["type"] == "mlstm"])
 def test_matrix_memory_with_every_prompt_kernel(models, dtype, staged, lanes, name, layer):
-    """The recurrence over a prompt with the plain kernel, with tokens staged in shared memory at 8
-    and at 32 lanes per column (sizes whose rows are not aligned fall back to the plain kernel by
+    """The recurrence over a prompt with the plain kernel, with tokens staged in shared memory at 8,
+    16 and 32 lanes per column (sizes whose rows are not aligned fall back to the plain kernel by
     themselves): a prompt longer than several stages, cut so that a stage is left partly filled,
     then continued token by token from the state the prompt left."""
     from thing_htn_2026_b200 import ops

@@ -28,7 +28,7 @@
 #include "common.cuh"
 
 static int g_mlstm_staged = 1;       // 0: steps of several tokens run the kernel without staging too (measurement)
-static int g_mlstm_lanes = 0;        // lanes per column in the staged kernel: 8, 32, or 0: by the step's size
+static int g_mlstm_lanes = 0;        // lanes per column in the staged kernel: 8, 16, 32, or 0: by the step's size
 
 namespace {
 
@@ -41,6 +41,13 @@ constexpr int kThreads = kLanes * kColumns;
 // gather float32 roundings that a cancelling n . q magnifies (the state in memory is float32).
 template <typename T> struct Carry { using type = float; };
 template <> struct Carry<float> { using type = double; };
+
+// Two adjacent entries at once (the address is a multiple of their joint size).
+template <typename T> __device__ __forceinline__ float2 load_pair(const T* p);
+template <> __device__ __forceinline__ float2 load_pair<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 load_pair<__nv_bfloat16>(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
 
 __device__ __forceinline__ float log_input_gate(float x, float cap) { return cap * tanhf(x / cap); }
 __device__ __forceinline__ float log_forget_gate(float y, float cap) {
@@ -137,10 +144,12 @@ __global__ void __launch_bounds__(kThreads) mlstm_recurrence_kernel(
 // exponentials of a token are then computed by one thread each.  Inside a stage a token costs a
 // column's lanes their multiply-adds, three shuffles per sum and one division.  The arithmetic,
 // and its order, are those of the kernel above.  Needs rows whose q, k and v parts start on
-// 16-byte boundaries (the launcher checks).  LANES lanes hold a column: 8, or 32 where a step has
-// no more (sequence, head, 16 columns) blocks than the GPU has SMs, so that 8 lanes would leave
-// every scheduler a single warp (0.92 against 1.00 ms for one prompt of 2,048 tokens with 16 heads
-// of 128 x 128; with 32 heads 8 lanes are ahead, 1.17 against 1.55 ms).
+// 16-byte boundaries (the launcher checks).  A lane takes pairs of adjacent
+// entries (one 4-byte load for two bfloat16), and q's scale multiplies the two sums, not every
+// entry.  LANES lanes hold a column: 8; 16 and 32 are built for measurement (one prompt of 2,048
+// tokens, 16 heads of 128 x 128: 0.80 ms at 8 lanes, 0.80 at 16, 0.89 at 32; 32 heads: 0.98, 1.07,
+// 1.46; eight prompts of 16 heads: 2.6, 3.2, 4.8: more lanes give more warps and more instructions
+// for the same sums, and no shorter chain per token).
 constexpr int kStage = 16;
 
 __device__ __forceinline__ void copy16_async(void* smem, const void* gmem) {
@@ -152,7 +161,7 @@ __device__ __forceinline__ void copy4_async(void* smem, const void* gmem) {
 __device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 __device__ __forceinline__ void copy_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 
-template <typename T, int R, int LANES>
+template <typename T, int R, int LANES, bool EXACT>
 __global__ void __launch_bounds__(LANES * kColumns) mlstm_recurrence_staged_kernel(
     float* __restrict__ o, float* __restrict__ S, float* __restrict__ nm, const T* __restrict__ proj, int proj_width,
     const float* __restrict__ gates, const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int n_heads, int D,
@@ -179,10 +188,12 @@ __global__ void __launch_bounds__(LANES * kColumns) mlstm_recurrence_staged_kern
     float* s_col = S + (((size_t)slot * n_heads + head) * E + (active ? column : 0)) * D;
     float* nm_block = nm + (((size_t)slot * n_heads + head) * gridDim.z + block_of_columns) * (D + 1);
     using A = typename Carry<T>::type;
+    // a lane holds the entries 2 lane + 2 LANES j and the one after it, j = 0 .. R / 2 - 1 (D is even here)
+    static_assert(R % 2 == 0, "pairs of entries");
     A s[R], n[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int d = lane + LANES * r;
+        const int d = 2 * lane + 2 * LANES * (r >> 1) + (r & 1);
         s[r] = active && d < D ? (A)s_col[d] : (A)0;
         n[r] = d < D ? (A)nm_block[d] : (A)0;
     }
@@ -233,23 +244,32 @@ __global__ void __launch_bounds__(LANES * kColumns) mlstm_recurrence_staged_kern
         m = running;
         __syncthreads();
         const T* stage = buffers + (size_t)buffer * stage_tokens * row_elems;
+        // (Unrolling this loop by four, so that the sums, shuffles and divisions of neighbouring tokens
+        // might overlap, made it slower: 0.97 against 0.85 ms for 2,048 tokens at 8 lanes.)
         for (int t = 0; t < count; ++t) {
             const T* q_src = stage + (size_t)t * row_elems;
             const T* k_src = q_src + D;
             const float v = active ? to_f32<T>(q_src[2 * D + group]) : 0.f;
             const float keep = keep_s[t], take = take_s[t];
-            A top = 0, bottom = 0;
+            A top = 0, bottom = 0, top1 = 0, bottom1 = 0;
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int d = lane + LANES * r;
-                const float k = d < D ? to_f32<T>(k_src[d]) : 0.f;
-                const float q = d < D ? to_f32<T>(q_src[d]) * q_scale : 0.f;
-                const A tk = (A)take * k;
-                s[r] = (A)keep * s[r] + tk * v;
-                n[r] = (A)keep * n[r] + tk;
-                top += s[r] * q;
-                bottom += n[r] * q;
+            for (int j = 0; j < R / 2; ++j) {
+                const int d = 2 * lane + 2 * LANES * j;
+                const bool inside = EXACT || d < D;       // EXACT: the lanes' entries are exactly the key's (D = LANES * R)
+                const float2 k = inside ? load_pair<T>(k_src + d) : make_float2(0.f, 0.f);
+                const float2 q = inside ? load_pair<T>(q_src + d) : make_float2(0.f, 0.f);
+                const A tk0 = (A)take * k.x, tk1 = (A)take * k.y;
+                s[2 * j] = (A)keep * s[2 * j] + tk0 * v;
+                s[2 * j + 1] = (A)keep * s[2 * j + 1] + tk1 * v;
+                n[2 * j] = (A)keep * n[2 * j] + tk0;
+                n[2 * j + 1] = (A)keep * n[2 * j + 1] + tk1;
+                top += s[2 * j] * q.x;
+                top1 += s[2 * j + 1] * q.y;
+                bottom += n[2 * j] * q.x;
+                bottom1 += n[2 * j + 1] * q.y;
             }
+            top = (top + top1) * (A)q_scale;          // q's scale, once for the sum
+            bottom = (bottom + bottom1) * (A)q_scale;
 #pragma unroll
             for (int w = LANES / 2; w > 0; w >>= 1) {
                 top += __shfl_xor_sync(0xffffffffu, top, w);
@@ -262,7 +282,7 @@ __global__ void __launch_bounds__(LANES * kColumns) mlstm_recurrence_staged_kern
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int d = lane + LANES * r;
+        const int d = 2 * lane + 2 * LANES * (r >> 1) + (r & 1);
         if (d < D) {
             if (active) s_col[d] = (float)s[r];
             if (group == 0) nm_block[d] = (float)n[r];
@@ -289,19 +309,31 @@ int launch_recurrence(float* o, float* S, float* nm, const void* proj, int proj_
         const int stage_tokens = std::max(1, std::min(kStage, 32768 / (2 * row_bytes)));
         const size_t smem = (size_t)2 * stage_tokens * row_bytes + 7 * kStage * sizeof(float);
 #define THN_MLSTM_STAGED(R, LANES)                                                                                     \
-    thn_launch_ordered(mlstm_recurrence_staged_kernel<T, R, LANES>, grid, LANES * kColumns, smem, stream, o, S, nm,     \
-                       (const T*)proj, proj_width, gates, cu_seqlens, slots, n_heads, D, E, q_scale, floor_, stage_tokens)
-        int sms = 148;
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
-        const long long blocks = (long long)grid.x * grid.y * grid.z;
-        const bool wide = g_mlstm_lanes == 32 || (g_mlstm_lanes == 0 && D >= 32 && blocks <= sms);
-        if (wide) {
+    do {                                                                                                               \
+        if (D == LANES * R)                                                                                            \
+            thn_launch_ordered(mlstm_recurrence_staged_kernel<T, R, LANES, true>, grid, LANES * kColumns, smem, stream, \
+                               o, S, nm, (const T*)proj, proj_width, gates, cu_seqlens, slots, n_heads, D, E, q_scale,  \
+                               floor_, stage_tokens);                                                                   \
+        else                                                                                                           \
+            thn_launch_ordered(mlstm_recurrence_staged_kernel<T, R, LANES, false>, grid, LANES * kColumns, smem, stream, \
+                               o, S, nm, (const T*)proj, proj_width, gates, cu_seqlens, slots, n_heads, D, E, q_scale,  \
+                               floor_, stage_tokens);                                                                   \
+    } while (0)
+        int lanes = g_mlstm_lanes;
+        if (lanes == 0) lanes = 8;
+        if (lanes == 32) {
             const int per32 = (D + 31) / 32;
-            if (per32 <= 1) THN_MLSTM_STAGED(1, 32);
-            else if (per32 <= 2) THN_MLSTM_STAGED(2, 32);
+            if (per32 <= 2) THN_MLSTM_STAGED(2, 32);
             else if (per32 <= 4) THN_MLSTM_STAGED(4, 32);
             else if (per32 <= 8) THN_MLSTM_STAGED(8, 32);
             else THN_MLSTM_STAGED(16, 32);
+        } else if (lanes == 16) {
+            const int per16 = (D + 15) / 16;
+            if (per16 <= 2) THN_MLSTM_STAGED(2, 16);
+            else if (per16 <= 4) THN_MLSTM_STAGED(4, 16);
+            else if (per16 <= 8) THN_MLSTM_STAGED(8, 16);
+            else if (per16 <= 16) THN_MLSTM_STAGED(16, 16);
+            else THN_MLSTM_STAGED(32, 16);
         } else if (per_lane <= 2) THN_MLSTM_STAGED(2, 8);
         else if (per_lane <= 4) THN_MLSTM_STAGED(4, 8);
         else if (per_lane <= 8) THN_MLSTM_STAGED(8, 8);
@@ -330,7 +362,7 @@ THN_API int thn_mlstm_columns_per_block() { return kColumns; }
 
 THN_API void thn_set_mlstm_staged(int on, int lanes) {
     g_mlstm_staged = on ? 1 : 0;
-    g_mlstm_lanes = lanes == 8 || lanes == 32 ? lanes : 0;
+    g_mlstm_lanes = lanes == 8 || lanes == 16 || lanes == 32 ? lanes : 0;
 }
 
 // pre [rows, 2 * heads] (x of every head, then y of every head), biases [heads]; out the same

@@ -1068,7 +1068,7 @@ def mlstm_column_blocks(value_dim: int) -> int:
 
 def set_mlstm_kernel(staged: bool = True, lanes: int = 0) -> None:
     """Which kernel steps of several tokens take (tests and measurement): the one that stages
-    tokens in shared memory or the plain one; 8 or 32 lanes per column, or 0: by the step's size."""
+    tokens in shared memory or the plain one; 8, 16 or 32 lanes per column, or 0: by the step's size."""
     lib().thn_set_mlstm_staged(int(bool(staged)), int(lanes))
 
 
