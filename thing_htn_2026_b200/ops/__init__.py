@@ -65,7 +65,7 @@ _SIGNATURES = {
     "thn_latent_norm": [c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_int, c_int, c_int, c_void_p],
     "thn_latent_assemble": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_void_p, c_void_p],
+                            c_int, c_void_p, c_void_p],
     "thn_mlstm_columns_per_block": [],
     "thn_mlstm_gates": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
     "thn_mlstm_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
@@ -94,11 +94,11 @@ _SIGNATURES = {
     "thn_attention_mma_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_fused_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
-                                   c_void_p],
+                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_void_p],
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_longlong,
-                                  c_int, c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_longlong, c_int, c_void_p, c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
     "thn_attention_decode_cluster_splits": [],
     "thn_attention_decode_one_wave_splits": [c_int, c_int, c_int],
@@ -741,18 +741,22 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
     kernels for steps of several tokens per sequence need ``tiles``.  With a window,
     ``keep_first`` keys at the start of a sequence stay visible to every later row.  With
     ``chunk`` a row sees the keys of its own chunk of that many positions only.
-    ``exact_weights`` asks for float32 softmax weights in the product with the values, which
-    the kernels without tensor cores honour."""
+    ``exact_weights`` asks for softmax weights that are not rounded to bfloat16 in the product
+    with the values: float32 in the kernel without tensor cores, two bfloat16 parts (the weight's
+    rounding and what the rounding left) in the ``mma.sync`` kernels; the tcgen05 prompt kernel,
+    which has neither, is then not taken."""
     keep_first = int(keep_first or 0) if window else 0
     if kv.v_dim != kv.head_dim:
         return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights)
     if q.dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
         if rows.max_q_len == 1:
-            return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first, chunk=chunk)
+            return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first, chunk=chunk,
+                                         split_weights=exact_weights)
         if tiles is not None:
-            if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
+            if not exact_weights and USE_TCGEN05_ATTENTION \
+                    and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
                 return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk)
-            return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk)
+            return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk, exact_weights)
     return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights)
 
 
@@ -788,15 +792,16 @@ def _check_tiles(tiles: RowTiles) -> None:
 
 def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
                            window: Optional[int], err: torch.Tensor, keep_first: int = 0,
-                           chunk: Optional[int] = None) -> torch.Tensor:
-    """Tensor-core flash attention for steps with several tokens per sequence."""
+                           chunk: Optional[int] = None, split_weights: bool = False) -> torch.Tensor:
+    """Tensor-core flash attention for steps with several tokens per sequence.  ``split_weights``:
+    the softmax weights multiply the values as two bfloat16 parts (two products), not one."""
     _need(q, "attention q", torch.bfloat16)
     out = torch.empty_like(q)
     _check_tiles(tiles)
     _call("thn_attention_prefill_bf16", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
           tiles.n, _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
           kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale), int(window or 0),
-          int(keep_first or 0), int(chunk or 0), _ptr(err), _stream())
+          int(keep_first or 0), int(chunk or 0), int(bool(split_weights)), _ptr(err), _stream())
     return out
 
 
@@ -859,7 +864,7 @@ def decode_hints(rows: StepRows, n_kv: int, n_splits: int, device) -> int:
 def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
                           window: Optional[int], err: torch.Tensor, n_splits: Optional[int] = None,
                           scratch: Optional[torch.Tensor] = None, fused_merge: bool = True,
-                          keep_first: int = 0, chunk: Optional[int] = None) -> torch.Tensor:
+                          keep_first: int = 0, chunk: Optional[int] = None, split_weights: bool = False) -> torch.Tensor:
     """Split-KV flash decoding: one token per sequence.  Partial results of the splits go
     through float32 scratch memory, which is allocated here unless given."""
     _need(q, "attention q", torch.bfloat16)
@@ -876,8 +881,8 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     out = torch.empty_like(q)
     _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
-          n_seqs, n_q, n_splits, float(scale), int(window or 0), int(keep_first or 0), int(chunk or 0), _ptr(scratch),
-          _ptr(counters),
+          n_seqs, n_q, n_splits, float(scale), int(window or 0), int(keep_first or 0), int(chunk or 0),
+          int(bool(split_weights)), _ptr(scratch), _ptr(counters),
           kv.storage.shape[0], decode_hints(rows, kv.n_kv, n_splits, q.device), _ptr(err), _stream())
     return out
 
@@ -1026,19 +1031,24 @@ def latent_norm(proj: torch.Tensor, offset: int, rank: int, gain: torch.Tensor, 
 
 def latent_assemble(proj: torch.Tensor, q_offset: int, shared_offset: int, up: torch.Tensor,
                     rotary: Optional[RotaryTables], rows: StepRows, kv: KVView, n_heads: int, plain: int, rot: int,
-                    err: torch.Tensor) -> torch.Tensor:
+                    err: torch.Tensor, value_dim: Optional[int] = None) -> torch.Tensor:
     """Queries and cache entries of latent attention.  ``proj`` rows hold the queries
     ``[heads][plain | rot]`` from column ``q_offset`` and one shared key part of ``rot`` entries
     from column ``shared_offset``; ``up`` [rows, heads * plain + heads * value] is the
     up-projection of the normalised latent.  The ``rot`` parts are rotated by the rows' positions
     (interleaved pairs); the cache gets per head the key ``[plain | rotated shared part]`` and the
-    value.  Returns the queries [rows, heads * (plain + rot)]."""
+    value.  ``value_dim`` (default: the cache's value size) is the size of a value in ``up``; a
+    cache whose values are wider gets zeros behind them.  Returns the queries
+    [rows, heads * (plain + rot)]."""
     _need(proj, "latent_assemble proj")
     _need(up, "latent_assemble up", proj.dtype)
     if kv.storage.dtype != proj.dtype or kv.n_kv != n_heads or kv.head_dim != plain + rot:
         raise KernelError(f"latent_assemble: the cache entry ({kv.n_kv} heads of {kv.head_dim}, {kv.storage.dtype}) does "
                           f"not fit {n_heads} heads of {plain} + {rot}, {proj.dtype}")
-    if proj.shape[0] != rows.n_rows or tuple(up.shape) != (rows.n_rows, n_heads * (plain + kv.v_dim)):
+    value_dim = kv.v_dim if value_dim is None else int(value_dim)
+    if value_dim > kv.v_dim:
+        raise KernelError(f"latent_assemble: values of {value_dim} do not fit the cache's {kv.v_dim}")
+    if proj.shape[0] != rows.n_rows or tuple(up.shape) != (rows.n_rows, n_heads * (plain + value_dim)):
         raise KernelError(f"latent_assemble: shapes proj {tuple(proj.shape)}, up {tuple(up.shape)} for {rows.n_rows} rows")
     if rot and (rotary is None or rotary.layout != "interleaved" or rotary.rotary_dim != rot):
         raise KernelError("latent_assemble: the rotated part needs interleaved tables of its size")
@@ -1048,7 +1058,7 @@ def latent_assemble(proj: torch.Tensor, q_offset: int, shared_offset: int, up: t
           proj.data_ptr() + shared_offset * size, proj.shape[1], _ptr(up), _ptr(rotary.cos) if rot else None,
           _ptr(rotary.sin) if rot else None, rotary.cos.shape[0] if rot else 0, _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.page_size, rows.n_rows, n_heads, plain, rot,
-          kv.v_dim, _code(proj, "latent_assemble"), _ptr(err), _stream())
+          kv.v_dim, value_dim, _code(proj, "latent_assemble"), _ptr(err), _stream())
     return q
 
 

@@ -18,8 +18,11 @@ i sees j with 0 <= i - j < window.  ``gated`` False leaves the output gate (and 
 One product gives q, the latent row and the gate (weights concatenated ``[q; dkv; g]``); a
 second one, on the normalised latent, gives every head's unrotated key and value (``[uk; uv]``).
 The cache holds per head the assembled key and the value (a window bounds what a sequence
-holds), so the attention kernels of the other mixers serve this one unchanged.  Kernels:
-csrc/latent_prepare.cu.
+holds), so the attention kernels of the other mixers serve this one unchanged.  Where the values
+are smaller than the keys and the tensor-core attention kernels take the keys' size (bfloat16),
+the cache's values are padded to that size with zeros, and the gate's rows and the output
+projection's columns with them, so that those kernels serve such sizes too; the result is the
+same, entry by entry.  Kernels: csrc/latent_prepare.cu.
 """
 
 from __future__ import annotations
@@ -29,7 +32,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
-from ..cache.sequence_cache import CacheNeed, KVSpec
+from ..cache.sequence_cache import PAGE_SIZE, CacheNeed, KVSpec
 from ..config.base import PartSpec, ScheduleEntry
 from ..weights.loader import GAIN, MATRIX, TensorSpec
 from .registry import part_class, register_part
@@ -68,12 +71,26 @@ class LatentAttention:
         self.gated = bool(p.get("gated", True))
         self.exact_weights = p.get("softmax_weights") == "float32"
         self.dtype = runtime.dtype
+        # the size of a value in the cache and in the attention's output: its own, or the keys'
+        key_dim, hidden = self.plain + self.rot, int(p["hidden_size"])
+        self.out_dim = self.value_dim
+        if runtime.dtype == torch.bfloat16 and self.value_dim < key_dim and p.get("pad_values", True) \
+                and ops.lib().thn_attention_mma_supported(key_dim, PAGE_SIZE, self.n_heads, self.n_heads):
+            self.out_dim = key_dim
+        pad = self.out_dim - self.value_dim
         parts = [runtime.tensor(spec, "q_proj"), runtime.tensor(spec, "down_proj")]
         if self.gated:
-            parts.append(runtime.tensor(spec, "g_proj"))
+            gate = runtime.tensor(spec, "g_proj")
+            if pad:
+                gate = torch.nn.functional.pad(gate.view(self.n_heads, self.value_dim, hidden), (0, 0, 0, pad))
+                gate = gate.reshape(self.n_heads * self.out_dim, hidden)
+            parts.append(gate)
         self.w_in = torch.cat(parts, dim=0).contiguous()
         self.w_up = torch.cat([runtime.tensor(spec, "up_k"), runtime.tensor(spec, "up_v")], dim=0).contiguous()
         self.w_o = runtime.tensor(spec, "o_proj")
+        if pad:
+            self.w_o = torch.nn.functional.pad(self.w_o.view(hidden, self.n_heads, self.value_dim), (0, pad))
+            self.w_o = self.w_o.reshape(hidden, self.n_heads * self.out_dim).contiguous()
         self.latent_gain = runtime.tensor(spec, "latent_norm").to(torch.float32).contiguous()
         self.latent_offset = self.n_heads * (self.plain + self.rot)
         self.shared_offset = self.latent_offset + self.rank
@@ -89,11 +106,11 @@ class LatentAttention:
             self.position = runtime.shared[key]
 
     def cache_need(self) -> CacheNeed:
-        return KVSpec(self.n_heads, self.plain + self.rot, self.window, 0, None, self.value_dim)
+        return KVSpec(self.n_heads, self.plain + self.rot, self.window, 0, None, self.out_dim)
 
     def _tile(self, page_size: int) -> int:
         return ops.prompt_attention_tile(self.dtype, self.plain + self.rot, page_size, self.n_heads, self.n_heads,
-                                         self.value_dim)
+                                         self.out_dim)
 
     def step_inputs(self, batch: HostBatch, out: Dict[str, List[int]]) -> None:
         """Row tiles for the tensor-core prompt kernel, where keys and values have one size that it
@@ -115,7 +132,7 @@ class LatentAttention:
         latent = ops.latent_norm(proj, self.latent_offset, self.rank, self.latent_gain, self.eps)
         up = ops.linear(latent, self.w_up, err=ctx.err)
         q = ops.latent_assemble(proj, 0, self.shared_offset, up, self.position.tables() if self.position else None,
-                                ctx.rows, kv, self.n_heads, self.plain, self.rot, ctx.err)
+                                ctx.rows, kv, self.n_heads, self.plain, self.rot, ctx.err, self.value_dim)
         a = ops.attention(q, ctx.rows, kv, self.n_heads, self.scale, self.window, ctx.err, tiles,
                           exact_weights=self.exact_weights)
         if self.gated:
