@@ -745,7 +745,7 @@ def bunudra_kernel_table(torch, bun, peak, batch, context):
         row(f"{tag}: logistic_gate", lambda: ops.logistic_gate(a16, g16, 64), nbytes=n * Hl * El * 6, like=f"{tag}: clamped_glu")
 
     # ---- attention over a paged cache: one sequence of T tokens, then `batch` sequences at `context` keys
-    def attention_rows(tag, spec, H, prepare_of, chunk, window, keep, likes):
+    def attention_rows(tag, spec, H, prepare_of, chunk, window, keep, likes, exact=False):
         n_slots = batch + 1
         cache = SequenceCache([spec], max_tokens=(batch * (context + 64) + T + 64), dtype=bf, device=dev, max_slots=n_slots + 1)
         slots = cache.open(n_slots)
@@ -773,8 +773,17 @@ def bunudra_kernel_table(torch, bun, peak, batch, context):
         seen = sum(i - first(i) + 1 + (min(keep, first(i)) if window else 0) for i in range(T))
         row(f"prefill: {tag[0]}", lambda: prepare(rows_), nbytes=prep_bytes(T), like=likes[0])
         q = prepare(rows_)
-        row(f"prefill: {tag[1]}", lambda: ops.attention(q, rows_, cache.kv_view(0), H, D ** -0.5, window, err, tiles, keep, chunk),
+        row(f"prefill: {tag[1]}", lambda: ops.attention(q, rows_, cache.kv_view(0), H, D ** -0.5, window, err, tiles, keep, chunk, exact),
             flops=4.0 * H * D * seen, nbytes=T * H * D * 4, like=likes[1])
+        if exact:      # the same on the mma.sync kernel, which takes the weights as two bfloat16 parts
+            def two_parts():
+                ops.USE_TCGEN05_ATTENTION = False
+                try:
+                    return ops.attention(q, rows_, cache.kv_view(0), H, D ** -0.5, window, err, tiles, keep, chunk, True)
+                finally:
+                    ops.USE_TCGEN05_ATTENTION = True
+            row(f"prefill: {tag[1]}, weights in two parts (mma.sync)", two_parts, flops=4.0 * H * D * seen,
+                nbytes=T * H * D * 4, like=likes[1])
         others = slots[1:]
         rows_, cu_dev, slots_dev = step_of(others, [context] * batch)
         prepare_c, _ = prepare_of(cache, batch * context)
@@ -786,7 +795,7 @@ def bunudra_kernel_table(torch, bun, peak, batch, context):
         row(f"decode: {tag[0]}", lambda: prepare_1(rows_), nbytes=prep_bytes(batch), like=likes[2])
         q1 = prepare_1(rows_)
         keys = context + 1 - first(context) + (min(keep, first(context)) if window else 0)
-        row(f"decode: {tag[1]}", lambda: ops.attention(q1, rows_, cache.kv_view(0), H, D ** -0.5, window, err, None, keep, chunk),
+        row(f"decode: {tag[1]}", lambda: ops.attention(q1, rows_, cache.kv_view(0), H, D ** -0.5, window, err, None, keep, chunk, exact),
             nbytes=batch * G * keys * D * 2 * 2, like=likes[3])
 
     H, G, D = attn["heads"], attn["kv_heads"], attn["dim"]
@@ -812,7 +821,7 @@ def bunudra_kernel_table(torch, bun, peak, batch, context):
     likes = tuple(f"{t}: {x}" for t in ("prefill", "decode") for x in lanilix_tags)
     likes = (likes[0], likes[1], likes[2], likes[3])
     attention_rows(("qk_prepare (head norm, rotate-half)", f"attention (chunks of {size})"), KVSpec(G, D, None, 0, size), H,
-                   head_norm_prepare, size, None, 0, likes)
+                   head_norm_prepare, size, None, 0, likes, exact=True)
 
     Hl, P, R, El, C = lat["heads"], lat["dim"], lat["rot_dim"], lat["vdim"], lat["kv_rank"]
     lat_tables = ops.RotaryTables(torch.ones(8192, R // 2, device=dev), torch.zeros(8192, R // 2, device=dev), R, "interleaved")
@@ -829,7 +838,8 @@ def bunudra_kernel_table(torch, bun, peak, batch, context):
         return run, lambda m: m * ((Hl * (P + R) + 2 * C + R + Hl * (P + El)) * 2 + (Hl * (P + R) + Hl * (P + R + El)) * 2)
 
     attention_rows(("latent_norm + latent_assemble", f"attention (latent heads, window {lat['mask']['size']})"),
-                   KVSpec(Hl, P + R, lat["mask"]["size"], 0, None, El), Hl, latent_prepare, None, lat["mask"]["size"], 0, likes)
+                   KVSpec(Hl, P + R, lat["mask"]["size"], 0, None, El), Hl, latent_prepare, None, lat["mask"]["size"], 0, likes,
+                   exact=True)
 
     # ---- the matrix memory against the delta rule: a prompt of T tokens, a step of `batch` sequences, `batch` prompts
     Hm, dk, dv = mem["heads"], mem["dim"], mem["vdim"]
