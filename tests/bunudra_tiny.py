@@ -78,6 +78,18 @@ CONFIGS = {
          "mlp": moe(9, 4, 30, groups=(3, 2), scale=2.5, shared=50)},
         {"type": "attention", "mixer": attention(2, 2, 12, 20, 0.25), "mlp": None},
     ]),
+    # what a file may leave out, and the largest sizes: chunks of exactly a page with full rotation; a
+    # latent attention without a window on keys of 64 with values of 48 (padded for the tensor-core
+    # kernels in bfloat16); one head with a key of 264 (64 state registers per lane); an attention
+    # without rotation and without a mask on one kv head for four heads; every expert chosen, no groups,
+    # no shared expert; one kept group whose experts are all chosen
+    "d": dict(vocab=97, width=40, eps=1e-6, emb=7.0, seed=24, layers=[
+        {"type": "attention", "mixer": attention(2, 2, 48, 48, 0.15, rot=(48, 1000000.0), chunk=64), "mlp": moe(5, 5, 24)},
+        {"type": "latent_attention", "mixer": latent(3, 48, 16, 48, 24, 0.14, 500000.0, scaling=(8.0, 32, 16.0, 2.0)),
+         "mlp": moe(6, 3, 16, groups=(2, 1), scale=1.0, shared=16)},
+        {"type": "mlstm", "mixer": mlstm(1, 264, 8, 10.0), "mlp": moe(5, 5, 24)},
+        {"type": "attention", "mixer": attention(4, 1, 32, 32, 0.2), "mlp": moe(6, 3, 16, groups=(2, 1), scale=1.0, shared=16)},
+    ]),
 }
 
 
